@@ -1,0 +1,561 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory ->
+// tcgen05.mma (UMMA 128x256x16, fp32 accumulators in TMEM, double-buffered) -> tcgen05.ld
+// epilogue with bias / GELU / GELU-grad / residual / column-sum / bf16|fp32|atomic stores.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. 32*(w%4)+31).
+//
+// This one kernel covers every dense and expert matmul of the model: forward (x W^T), dgrad
+// (dy W, B read MN-major) and wgrad (dy^T x, both operands MN-major, split-K with fp32
+// atomics), batched over experts through the third TMA coordinate. It replaces the matmuls
+// that the reference leaves to XLA (vmoe/nn/vit_moe.py:38-45 MlpBlock, vmoe/moe.py:429-444
+// vmapped experts).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "ptx_sm100.cuh"
+#include "vmoe_api.h"
+
+namespace vmoe {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int CHUNK_BYTES = 64 * BK * 2;    // one 64 x 64 MN-major box = 8 KiB
+constexpr int TMEM_COLS = 512;              // two 128 x 256 fp32 accumulators
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256;
+
+struct GemmParams {
+  void* C;
+  void* C2;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  const __nv_bfloat16* gelu_pre;
+  float* colsum;
+  const unsigned* a_ready;
+  unsigned* status;
+  long long ldc, ldr, ldr2;
+  long long c_batch_stride, bias_batch_stride, r_batch_stride;
+  int M, N, K, batch;
+  int a_mn_major, b_mn_major;
+  int c_fp32, c_atomic, act, split_k;
+  unsigned a_ready_epoch;
+};
+
+struct TileCoord {
+  int b, mt, nt, ks;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(int tile, int num_m, int num_n, int split_k) {
+  // n fastest, then split, then m, then batch: CTAs that run together share an A panel
+  // through L2 while the (small) B matrix stays L2 resident.
+  TileCoord t;
+  t.nt = tile % num_n;
+  tile /= num_n;
+  t.ks = tile % split_k;
+  tile /= split_k;
+  t.mt = tile % num_m;
+  t.b = tile / num_m;
+  return t;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Sum v[i] over the 32 lanes of the warp for all 32 register columns with 31 shuffles; on
+// return lane L holds the total of column L in v[0].
+__device__ __forceinline__ void warp_transpose_reduce(float (&v)[32], int lane) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int j = 0; j < off; ++j) {
+      float send = upper ? v[j] : v[j + off];
+      float keep = upper ? v[j + off] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + STAGES);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * STAGES + 2);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 4);  // one arrival per epilogue warp
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int k_tiles = (p.K + BK - 1) / BK;
+  const int k_per_split = (k_tiles + p.split_k - 1) / p.split_k;
+  const int num_tiles = p.batch * num_m * num_n * p.split_k;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k);
+        const int m0 = t.mt * BM, n0 = t.nt * BN;
+        const int kt0 = t.ks * k_per_split;
+        const int kt1 = min(k_tiles, kt0 + k_per_split);
+        if (p.a_ready != nullptr && kt0 < kt1) {
+          // Rows of this A tile are produced by another kernel (possibly on a peer GPU) that
+          // adds the number of rows it wrote to a counter, release at system scope.
+          const unsigned rows = static_cast<unsigned>(min(BM, p.M - m0));
+          const unsigned want = p.a_ready_epoch * rows;
+          const unsigned* flag = p.a_ready + (static_cast<long long>(t.b) * num_m + t.mt);
+          const long long t0 = clock64();
+          while (static_cast<int>(ld_acquire_sys(flag) - want) < 0) {
+            if (*abort_flag || clock64() - t0 > kWaitLimitCycles) {
+              *abort_flag = 1;
+              if (p.status) atomicOr(p.status, kStatusTimeoutFlag);
+              ok = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        for (int kt = kt0; kt < kt1; ++kt) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status,
+                         kStatusTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
+          const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
+          const int k0 = kt * BK;
+          if (!p.a_mn_major) {
+            tma_load_3d(a_dst, &tma_a, full, k0, m0, t.b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(a_dst + j * CHUNK_BYTES, &tma_a, full, m0 + 64 * j, k0, t.b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(b_dst, &tma_b, full, k0, n0, t.b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * CHUNK_BYTES, &tma_b, full, n0 + 64 * j, k0, t.b);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Give copies that are still in flight a bounded chance to land before the CTA exits.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) __nanosleep(256);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+      // K-major: 8-row groups 1024 B apart, 32 B per UMMA_K step inside the swizzle row.
+      // MN-major: 64-element chunks CHUNK_BYTES apart (LBO), 8-row K groups 1024 B apart
+      // (SBO), 16 K rows = 2048 B per UMMA_K step.
+      const uint32_t a_lbo = p.a_mn_major ? CHUNK_BYTES : 16, a_step = p.a_mn_major ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn_major ? CHUNK_BYTES : 16, b_step = p.b_mn_major ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k);
+        const int kt0 = t.ks * k_per_split;
+        const int kt1 = min(k_tiles, kt0 + k_per_split);
+        const int slot = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        if (!mbar_wait(bar_tempty + 8 * slot, (use & 1) ^ 1, abort_flag, p.status,
+                       kStatusTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + slot * BN;
+        for (int kt = kt0; kt < kt1; ++kt) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kStatusTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = umma_smem_desc(a_addr + k * a_step, a_lbo, 1024);
+            const uint64_t bdesc = umma_smem_desc(b_addr + k * b_step, b_lbo, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kt > kt0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + 8 * slot);  // accumulator complete -> epilogue
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k);
+      const int kt0 = t.ks * k_per_split;
+      const int kt1 = min(k_tiles, kt0 + k_per_split);
+      const int slot = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1);
+      const bool got = mbar_wait(bar_tfull + 8 * slot, use & 1, abort_flag, p.status,
+                                 kStatusTimeoutEpilogue);
+      if (!__all_sync(0xffffffffu, got)) {  // warp-uniform so the aligned TMEM loads converge
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool empty_k = kt0 >= kt1;  // a split with no K tiles contributes nothing
+      const int row = t.mt * BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int n0 = t.nt * BN;
+      const long long crow = static_cast<long long>(t.b) * p.c_batch_stride +
+                             static_cast<long long>(row) * p.ldc;
+      const float* bias = p.bias ? p.bias + static_cast<long long>(t.b) * p.bias_batch_stride
+                                 : nullptr;
+      // Only the first split adds bias/residual so that atomically summed splits count them once.
+      const bool first_split = t.ks == 0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + slot * BN + c * 32,
+                      r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.0f : __uint_as_float(r[i]);
+        const bool full_cols = col0 + 32 <= p.N;
+        if (bias && first_split) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (full_cols || col0 + i < p.N) v[i] += __ldg(bias + col0 + i);
+        }
+        const bool vec_bf16 = full_cols && (p.ldc % 8 == 0);
+        if (p.C2 && row_ok) {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0;
+          if (vec_bf16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 q;
+              q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+              q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+              q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+              q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+              reinterpret_cast<uint4*>(out)[i] = q;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) out[i] = __float2bfloat16(v[i]);
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        }
+        if (p.gelu_pre && row_ok) {
+          const __nv_bfloat16* pre = p.gelu_pre + static_cast<long long>(t.b) * p.r_batch_stride +
+                                     static_cast<long long>(row) * p.ldr2 + col0;
+          if (full_cols && (p.ldr2 % 8 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 q = __ldg(reinterpret_cast<const uint4*>(pre) + i);
+              const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y);
+              const float2 f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+              v[8 * i + 0] *= gelu_tanh_grad(f0.x);
+              v[8 * i + 1] *= gelu_tanh_grad(f0.y);
+              v[8 * i + 2] *= gelu_tanh_grad(f1.x);
+              v[8 * i + 3] *= gelu_tanh_grad(f1.y);
+              v[8 * i + 4] *= gelu_tanh_grad(f2.x);
+              v[8 * i + 5] *= gelu_tanh_grad(f2.y);
+              v[8 * i + 6] *= gelu_tanh_grad(f3.x);
+              v[8 * i + 7] *= gelu_tanh_grad(f3.y);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] *= gelu_tanh_grad(__bfloat162float(pre[i]));
+          }
+        }
+        if (p.residual && row_ok && first_split) {
+          const __nv_bfloat16* res = p.residual + static_cast<long long>(t.b) * p.r_batch_stride +
+                                     static_cast<long long>(row) * p.ldr + col0;
+          if (full_cols && (p.ldr % 8 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 q = __ldg(reinterpret_cast<const uint4*>(res) + i);
+              const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y);
+              const float2 f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+              v[8 * i + 0] += f0.x;
+              v[8 * i + 1] += f0.y;
+              v[8 * i + 2] += f1.x;
+              v[8 * i + 3] += f1.y;
+              v[8 * i + 4] += f2.x;
+              v[8 * i + 5] += f2.y;
+              v[8 * i + 6] += f3.x;
+              v[8 * i + 7] += f3.y;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(res[i]);
+          }
+        }
+        if (row_ok) {
+          if (!p.c_fp32) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
+            if (vec_bf16) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 q;
+                q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+                q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+                reinterpret_cast<uint4*>(out)[i] = q;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) out[i] = __float2bfloat16(v[i]);
+            }
+          } else {
+            float* out = reinterpret_cast<float*>(p.C) + crow + col0;
+            if (p.c_atomic) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (full_cols || col0 + i < p.N) atomicAdd(out + i, v[i]);
+            } else if (full_cols && (p.ldc % 4 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(out)[i] =
+                    make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) out[i] = v[i];
+            }
+          }
+        }
+        if (p.colsum) {
+          if (!row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+          }
+          warp_transpose_reduce(v, lane);
+          if (col0 + lane < p.N)
+            atomicAdd(p.colsum + static_cast<long long>(t.b) * p.bias_batch_stride + col0 + lane,
+                      v[0]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, const char* a, int code) {
+  snprintf(g_err, sizeof(g_err), fmt, a, code);
+}
+
+static PFN_cuTensorMapEncodeTiled get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || ptr == nullptr) return nullptr;
+  fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(ptr);
+  return fn;
+}
+
+// bf16 matrix stored [batch][rows][ld] viewed as a 3-D tensor (inner, rows, batch) with a
+// 64-element (128 B) swizzled inner box.
+int make_bf16_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch,
+                  uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_rows) {
+  PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
+  if (!enc) {
+    set_error("%s (code %d)", "cuTensorMapEncodeTiled entry point not available", 0);
+    return -2;
+  }
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t strides[2] = {ld_elems * 2, (batch > 1 ? batch_stride_elems : rows * ld_elems) * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("%s (code %d)", "cuTensorMapEncodeTiled failed", static_cast<int>(r));
+    return -3;
+  }
+  return 0;
+}
+
+}  // namespace vmoe
+
+extern "C" const char* vmoe_last_error(void) { return vmoe::g_err; }
+
+extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
+  using namespace vmoe;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  g_err[0] = 0;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) return 0;  // nothing to do
+  if ((a->lda % 8) || (a->ldb % 8) || (reinterpret_cast<uintptr_t>(a->A) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->B) & 15) || (a->a_batch_stride % 8) ||
+      (a->b_batch_stride % 8)) {
+    set_error("%s (code %d)", "gemm operands must be 16-byte aligned with ld % 8 == 0", 0);
+    return -1;
+  }
+  if ((a->split_k > 1 || a->c_atomic) && !(a->c_fp32 && a->c_atomic)) {
+    set_error("%s (code %d)", "split_k / atomic output needs c_fp32 and c_atomic", 0);
+    return -1;
+  }
+  CUtensorMap ma, mb;
+  int rc;
+  if (!a->a_mn_major)
+    rc = make_bf16_map(&ma, a->A, a->K, a->M, a->batch, a->lda, a->a_batch_stride, BM);
+  else
+    rc = make_bf16_map(&ma, a->A, a->M, a->K, a->batch, a->lda, a->a_batch_stride, BK);
+  if (rc) return rc;
+  if (!a->b_mn_major)
+    rc = make_bf16_map(&mb, a->B, a->K, a->N, a->batch, a->ldb, a->b_batch_stride, BN);
+  else
+    rc = make_bf16_map(&mb, a->B, a->N, a->K, a->batch, a->ldb, a->b_batch_stride, BK);
+  if (rc) return rc;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.C = a->C;
+  p.C2 = a->C2;
+  p.bias = a->bias;
+  p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+  p.gelu_pre = static_cast<const __nv_bfloat16*>(a->gelu_pre);
+  p.colsum = a->colsum;
+  p.a_ready = a->a_ready;
+  p.status = a->status;
+  p.ldc = a->ldc;
+  p.ldr = a->ldr;
+  p.ldr2 = a->ldr2;
+  p.c_batch_stride = a->c_batch_stride;
+  p.bias_batch_stride = a->bias_batch_stride;
+  p.r_batch_stride = a->r_batch_stride;
+  p.M = static_cast<int>(a->M);
+  p.N = static_cast<int>(a->N);
+  p.K = static_cast<int>(a->K);
+  p.batch = static_cast<int>(a->batch);
+  p.a_mn_major = a->a_mn_major;
+  p.b_mn_major = a->b_mn_major;
+  p.c_fp32 = a->c_fp32;
+  p.c_atomic = a->c_atomic;
+  p.act = a->act;
+  p.split_k = a->split_k > 1 ? a->split_k : 1;
+  p.a_ready_epoch = a->a_ready_epoch;
+
+  static int sm_count = 0;
+  static bool attr_set = false;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
+      return -4;
+    }
+    attr_set = true;
+  }
+  const long long num_m = (a->M + BM - 1) / BM, num_n = (a->N + BN - 1) / BN;
+  const long long tiles = a->batch * num_m * num_n * p.split_k;
+  int max_ctas = a->num_sms > 0 ? a->num_sms : sm_count;
+  int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
+  gemm_bf16_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
+    return -5;
+  }
+  return 0;
+}
