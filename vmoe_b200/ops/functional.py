@@ -1,0 +1,209 @@
+"""Differentiable front-ends of the hot ops.
+
+Dispatch rule: a CUDA bf16 input with kernels enabled runs the sm_100a kernels (and raises if
+the library is missing — there is no silent fallback on a GPU); anything else runs PyTorch.
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from vmoe_b200.ops import _lib, reduce
+from vmoe_b200.ops.gemm import ACT_GELU, ACT_NONE, gemm
+
+_ENABLED = os.environ.get("VMOE_B200_KERNELS", "1") != "0"
+
+
+def cuda_kernels_enabled() -> bool:
+  return _ENABLED
+
+
+@contextlib.contextmanager
+def use_cuda_kernels(enabled: bool):
+  """Temporarily switches the CUDA kernels on/off (off = PyTorch library ops, the baseline)."""
+  global _ENABLED
+  prev, _ENABLED = _ENABLED, enabled
+  try:
+    yield
+  finally:
+    _ENABLED = prev
+
+
+def _fast(x: torch.Tensor) -> bool:
+  return _ENABLED and x.is_cuda and x.dtype == torch.bfloat16
+
+
+def bf16_shadow(p: torch.Tensor) -> torch.Tensor:
+  """bf16 copy of an fp32 master parameter, refreshed when the parameter changes.
+
+  The fused optimizer refreshes shadows in the same kernel that updates the master weights
+  (it bumps ``_shadow_version``), so the cast below only runs after out-of-band changes.
+  """
+  if p.dtype == torch.bfloat16:
+    return p.detach()
+  sh = getattr(p, "_bf16_shadow", None)
+  ver = p._version
+  if sh is None or getattr(p, "_shadow_version", -1) != ver or sh.shape != p.shape:
+    if sh is None or sh.shape != p.shape or sh.device != p.device:
+      sh = torch.empty_like(p, dtype=torch.bfloat16)
+      p._bf16_shadow = sh
+    sh.copy_(p.detach())
+    p._shadow_version = ver
+  return sh
+
+
+# ----------------------------------------------------------------------------------- linear
+class _LinearFn(torch.autograd.Function):
+  """y = act(x W^T + b) (+ residual) on the tcgen05 GEMM; backward = dgrad + wgrad GEMMs."""
+
+  @staticmethod
+  def forward(ctx, x, weight, bias, residual, act):
+    w16 = bf16_shadow(weight)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+      x2 = x2.contiguous()
+    need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    n = weight.shape[0]
+    pre = None
+    if act == ACT_GELU and need_grad:
+      pre = torch.empty(x2.shape[0], n, dtype=torch.bfloat16, device=x.device)
+    res2 = residual.reshape(-1, n) if residual is not None else None
+    y = gemm(x2, w16, bias=bias, act=act, residual=res2, out_pre=pre)
+    ctx.save_for_backward(x2, weight, pre)
+    ctx.has_bias = bias is not None
+    ctx.has_res = residual is not None
+    ctx.x_shape = x.shape
+    return y.reshape(*x.shape[:-1], n)
+
+  @staticmethod
+  def backward(ctx, dy):
+    x2, weight, pre = ctx.saved_tensors
+    w16 = bf16_shadow(weight)
+    n, k = weight.shape
+    dy2 = dy.reshape(-1, n)
+    if not dy2.is_contiguous():
+      dy2 = dy2.contiguous()
+    d_res = dy if ctx.has_res else None
+    if pre is not None:
+      # Stand-alone GELU linear layers are off the hot path (the MLP blocks use expert_mlp,
+      # whose dgrad GEMM applies gelu' in its epilogue).
+      from vmoe_b200.ops.gemm import gelu_tanh_grad
+      dy2 = (dy2.float() * gelu_tanh_grad(pre.float())).to(torch.bfloat16)
+    dbias = reduce.colsum(dy2) if ctx.has_bias else None
+    dx = None
+    if ctx.needs_input_grad[0]:
+      dx = gemm(dy2, w16, b_mn_major=True).reshape(ctx.x_shape)
+    dw = None
+    if ctx.needs_input_grad[1]:
+      dw = torch.zeros(n, k, dtype=torch.float32, device=dy.device)
+      m = dy2.shape[0]
+      gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=dw, accumulate=True,
+           split_k=_wgrad_split(n, k, m))
+    return dx, dw, dbias, d_res, None
+
+
+def _wgrad_split(n: int, k: int, m: int) -> int:
+  tiles = ((n + 127) // 128) * ((k + 255) // 256)
+  if tiles >= 120 or m < 4096:
+    return 1
+  return max(1, min(148 // tiles, m // 2048))
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+           act: Optional[str] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """``act(x @ weight^T + bias) + residual`` with ``weight: [out, in]``; ``act`` in {None, 'gelu'}."""
+  if _fast(x):
+    code = ACT_GELU if act == "gelu" else ACT_NONE
+    return _LinearFn.apply(x, weight, bias, residual, code)
+  y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+  if act == "gelu":
+    y = F.gelu(y, approximate="tanh")
+  if residual is not None:
+    y = y + residual
+  return y
+
+
+# ----------------------------------------------------------------------------------- expert MLP
+class _ExpertMlpFn(torch.autograd.Function):
+  """Batched (per local expert) GEMM1 + bias + GELU, GEMM2 + bias; rows fixed by capacity."""
+
+  @staticmethod
+  def forward(ctx, x, w1, b1, w2, b2, residual):
+    # x: (E, R, H) bf16; w1: (E, M, H); w2: (E, H, M)
+    w1h, w2h = bf16_shadow(w1), bf16_shadow(w2)
+    e, r, h = x.shape
+    m = w1.shape[1]
+    x = x.contiguous()
+    need_grad = torch.is_grad_enabled()
+    pre = torch.empty(e, r, m, dtype=torch.bfloat16, device=x.device) if need_grad else None
+    hid = gemm(x, w1h, bias=b1, act=ACT_GELU, out_pre=pre)
+    y = gemm(hid, w2h, bias=b2, residual=residual)
+    ctx.save_for_backward(x, w1, w2, pre, hid)
+    ctx.has_res = residual is not None
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, w1, w2, pre, hid = ctx.saved_tensors
+    w1h, w2h = bf16_shadow(w1), bf16_shadow(w2)
+    e, r, h = x.shape
+    m = w1.shape[1]
+    dy = dy.contiguous()
+    db2 = reduce.colsum(dy)
+    dw2 = torch.zeros(e, h, m, dtype=torch.float32, device=dy.device)
+    gemm(dy, hid, a_mn_major=True, b_mn_major=True, out=dw2, accumulate=True)
+    db1 = torch.zeros(e, m, dtype=torch.float32, device=dy.device)
+    dpre = gemm(dy, w2h, b_mn_major=True, gelu_pre=pre, colsum=db1)
+    dw1 = torch.zeros(e, m, h, dtype=torch.float32, device=dy.device)
+    gemm(dpre, x, a_mn_major=True, b_mn_major=True, out=dw1, accumulate=True)
+    dx = gemm(dpre, w1h, b_mn_major=True) if ctx.needs_input_grad[0] else None
+    return dx, dw1, db1, dw2, db2, (dy if ctx.has_res else None)
+
+
+def expert_mlp(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor,
+               b2: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """Per-expert MLP on ``x: (E_local, rows, H)`` with ``w1: (E, M, H)``, ``w2: (E, H, M)``.
+
+  ``residual`` (same shape as the output) is added in the second GEMM's epilogue.
+  """
+  if _fast(x):
+    return _ExpertMlpFn.apply(x, w1, b1, w2, b2, residual)
+  dt = x.dtype
+  hid = torch.baddbmm(b1.to(dt).unsqueeze(1), x, w1.to(dt).transpose(1, 2))
+  hid = F.gelu(hid, approximate="tanh")
+  y = torch.baddbmm(b2.to(dt).unsqueeze(1), hid, w2.to(dt).transpose(1, 2))
+  return y if residual is None else y + residual
+
+
+# ----------------------------------------------------------------------------------- layer norm
+def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+               eps: float = 1e-6) -> torch.Tensor:
+  if _fast(x) and x.shape[-1] % 8 == 0:
+    from vmoe_b200.ops import norm
+    return norm.layer_norm(x, weight, bias, eps)
+  w = None if weight is None else weight.to(x.dtype)
+  b = None if bias is None else bias.to(x.dtype)
+  return F.layer_norm(x, (x.shape[-1],), w, b, eps)
+
+
+# ----------------------------------------------------------------------------------- attention
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+              dropout_p: float = 0.0, training: bool = False) -> torch.Tensor:
+  """Non-causal softmax attention; ``q: (B, Tq, heads, d)``, ``k, v: (B, Tk, heads, d)``."""
+  d = q.shape[-1]
+  if (_fast(q) and not (training and dropout_p > 0) and d in (64, 80, 128)
+      and q.shape[1] == k.shape[1]):
+    from vmoe_b200.ops import attention as attn_ops
+    if attn_ops.supported(q, k, v):
+      return attn_ops.attention(q, k, v)
+  scale = 1.0 / math.sqrt(d)
+  logits = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
+  probs = torch.softmax(logits.float(), dim=-1).to(q.dtype)
+  if training and dropout_p > 0:
+    probs = F.dropout(probs, dropout_p, True)
+  return torch.einsum("bhqk,bkhd->bqhd", probs, v)
