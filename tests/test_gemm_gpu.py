@@ -1,0 +1,81 @@
+"""tcgen05 GEMM kernel vs an fp32 PyTorch reference of the same contract."""
+import pytest
+import torch
+
+from vmoe_b200.ops import gemm as G
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape):
+  return torch.randn(*shape, device=DEV).bfloat16()
+
+
+def _check(out, ref, tol=2e-2):
+  err = (out.float() - ref.float()).abs().max().item()
+  scale = ref.float().abs().max().item() + 1e-6
+  assert err / scale < tol, (err, scale)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (512, 768, 768), (200, 304, 136), (1000, 21843, 192)])
+@pytest.mark.parametrize("amn,bmn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_majors(m, n, k, amn, bmn):
+  if n % 8 and bmn:
+    pytest.skip("MN-major B needs a 16-byte aligned leading dimension")
+  torch.manual_seed(0)
+  a = _rand(k, m) if amn else _rand(m, k)
+  b = _rand(k, n) if bmn else _rand(n, k)
+  status = torch.zeros(1, dtype=torch.int32, device=DEV)
+  out = G.gemm(a, b, a_mn_major=amn, b_mn_major=bmn, status=status, out_dtype=torch.float32)
+  ref = G.gemm_reference(a, b, a_mn_major=amn, b_mn_major=bmn, out_dtype=torch.float32)
+  _check(out, ref, 1e-3)
+  assert status.item() == 0
+
+
+def test_gemm_batched_and_epilogue():
+  torch.manual_seed(1)
+  e, m, n, k = 3, 300, 520, 192
+  a, b = _rand(e, m, k), _rand(e, n, k)
+  bias = torch.randn(e, n, device=DEV)
+  res = _rand(e, m, n)
+  pre = torch.empty(e, m, n, device=DEV, dtype=torch.bfloat16)
+  cs = torch.zeros(e, n, device=DEV)
+  out = G.gemm(a, b, bias=bias, act=G.ACT_GELU, residual=res, out_pre=pre, colsum=cs)
+  pre_r = torch.empty_like(pre)
+  cs_r = torch.zeros_like(cs)
+  ref = G.gemm_reference(a, b, bias=bias, act=G.ACT_GELU, residual=res, out_pre=pre_r, colsum=cs_r,
+                         out_dtype=torch.float32)
+  _check(out, ref)
+  _check(pre, pre_r)
+  _check(cs, cs_r, 5e-3)
+
+
+def test_gemm_gelu_grad_and_splitk():
+  torch.manual_seed(2)
+  m, n, k = 300, 520, 1000
+  a, b = _rand(m, k), _rand(n, k)
+  gp = _rand(m, n)
+  out = G.gemm(a, b, gelu_pre=gp)
+  _check(out, G.gemm_reference(a, b, gelu_pre=gp, out_dtype=torch.float32))
+  o32 = torch.zeros(m, n, device=DEV)
+  G.gemm(a, b, out=o32, accumulate=True, split_k=3)
+  G.gemm(a, b, out=o32, accumulate=True)
+  _check(o32, 2 * G.gemm_reference(a, b, out_dtype=torch.float32), 1e-3)
+
+
+def test_gemm_ready_flag_timeout_sets_status():
+  """A flag that nothing sets must time out, report through the status word and return."""
+  import os
+  a, b = _rand(128, 64), _rand(256, 64)
+  flags = torch.zeros(1, dtype=torch.int32, device=DEV)
+  status = torch.zeros(1, dtype=torch.int32, device=DEV)
+  out = G.gemm(a, b, a_ready=flags, a_ready_epoch=1, status=status)
+  torch.cuda.synchronize()
+  assert status.item() & 8  # kStatusTimeoutFlag
+  # The context stays usable and a signalled flag lets the same call complete.
+  flags.fill_(128)
+  status.zero_()
+  out = G.gemm(a, b, a_ready=flags, a_ready_epoch=1, status=status, out_dtype=torch.float32)
+  _check(out, G.gemm_reference(a, b, out_dtype=torch.float32), 1e-3)
+  assert status.item() == 0

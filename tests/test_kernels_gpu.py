@@ -1,0 +1,167 @@
+"""Elementwise / MoE / loss / optimizer kernels vs PyTorch fp32 references."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from vmoe_b200 import moe as moe_core
+from vmoe_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, tol):
+  a, b = a.detach().float().cpu(), b.detach().float().cpu()
+  err = (a - b).abs().max().item()
+  scale = b.abs().max().item() + 1e-6
+  assert err / scale < tol, (err, scale)
+
+
+@pytest.mark.parametrize("h", [768, 1024, 1280, 64])
+def test_layer_norm(h):
+  torch.manual_seed(0)
+  x = (torch.randn(1000, h, device=DEV) * 2 + 0.5).bfloat16().requires_grad_()
+  w = torch.randn(h, device=DEV).requires_grad_()
+  b = torch.randn(h, device=DEV).requires_grad_()
+  y = ops.layer_norm(x, w, b, 1e-6)
+  dy = torch.randn_like(y)
+  y.backward(dy)
+  x2 = x.detach().float().requires_grad_()
+  w2, b2 = w.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+  y2 = F.layer_norm(x2, (h,), w2, b2, 1e-6)
+  y2.backward(dy.float())
+  _close(y, y2, 2e-2)
+  _close(x.grad, x2.grad, 2e-2)
+  _close(w.grad, w2.grad, 1e-2)
+  _close(b.grad, b2.grad, 1e-2)
+
+
+def test_colsum_and_patchify():
+  from vmoe_b200.ops import elementwise, reduce
+  torch.manual_seed(0)
+  x = torch.randn(3, 1000, 520, device=DEV).bfloat16()
+  _close(reduce.colsum(x), x.float().sum(1), 1e-3)
+  _close(reduce.colsum(x[0]), x[0].float().sum(0), 1e-3)
+  img = torch.rand(4, 64, 96, 3, device=DEV)
+  p = elementwise.patchify(img, 16, 16)
+  ref = img.reshape(4, 4, 16, 6, 16, 3).permute(0, 1, 3, 2, 4, 5).reshape(4, 24, 768)
+  _close(p, ref, 1e-2)
+
+
+@pytest.mark.parametrize("bpr", [False, True])
+@pytest.mark.parametrize("g,s,e,k,c", [(3, 40, 4, 2, 12), (2, 1576, 8, 2, 416), (2, 257, 32, 3, 16)])
+def test_routing_plan_matches_oracle(bpr, g, s, e, k, c):
+  from vmoe_b200.ops import moe_ops
+  torch.manual_seed(0)
+  gates = torch.softmax(torch.randn(g, s, e, device=DEV), -1)
+  expert, slot, slot_pair = moe_ops.routing_plan(gates, k, c, bpr)
+  plan = moe_core.top_experts_per_item_plan(gates.cpu(), k, c, bpr)
+  assert torch.equal(expert.cpu(), plan.expert)
+  assert torch.equal(slot.cpu(), plan.slot)
+  # slot_pair is the inverse map of the kept pairs.
+  sp = torch.full((g, e, c), -1, dtype=torch.int32)
+  for gi in range(g):
+    for si in range(s):
+      for ki in range(k):
+        p = int(plan.slot[gi, si, ki])
+        if p < c:
+          sp[gi, int(plan.expert[gi, si, ki]), p] = si * k + ki
+  assert torch.equal(slot_pair.cpu(), sp)
+
+
+def _moe_reference(x, gates_logits, w1, b1, w2, b2, res, k, c, bpr):
+  gates = torch.softmax(gates_logits, -1)
+  d = moe_core.get_top_experts_per_item_dispatcher(gates, "indices", k, bpr, capacity=c)
+  def mlp(xe):
+    h = F.gelu(torch.baddbmm(b1.unsqueeze(1), xe, w1.transpose(1, 2)), approximate="tanh")
+    return torch.baddbmm(b2.unsqueeze(1), h, w2.transpose(1, 2))
+  return moe_core.sparse_moe_apply(mlp, d, x) + res
+
+
+def test_fused_moe_layer_forward_backward():
+  from vmoe_b200.ops import moe_ops
+  torch.manual_seed(0)
+  g, s, h, m, e, k, c = 4, 64, 128, 256, 4, 2, 24
+  x = torch.randn(g, s, h, device=DEV).bfloat16().requires_grad_()
+  res = torch.randn(g, s, h, device=DEV).bfloat16().requires_grad_()
+  logits = torch.randn(g, s, e, device=DEV).requires_grad_()
+  w1 = (torch.randn(e, m, h, device=DEV) * 0.05).requires_grad_()
+  b1 = (torch.randn(e, m, device=DEV) * 0.1).requires_grad_()
+  w2 = (torch.randn(e, h, m, device=DEV) * 0.05).requires_grad_()
+  b2 = (torch.randn(e, h, device=DEV) * 0.1).requires_grad_()
+
+  class Mlp:
+    training = False
+    dropout_rate = 0.0
+  mlp = Mlp()
+  mlp.w1, mlp.b1, mlp.w2, mlp.b2 = w1, b1, w2, b2
+  gates = torch.softmax(logits, -1)
+  disp = moe_ops.FusedTopKDispatcher(gates, k, c, True)
+  y = disp.apply_experts(mlp, x, residual=res)
+  dy = torch.randn_like(y)
+  y.backward(dy)
+
+  ref_in = [t.detach().float().requires_grad_() for t in (x, logits, w1, b1, w2, b2, res)]
+  xr, lr, w1r, b1r, w2r, b2r, rr = ref_in
+  yr = _moe_reference(xr, lr, w1r, b1r, w2r, b2r, rr, k, c, True)
+  yr.backward(dy.float())
+  _close(y, yr, 3e-2)
+  _close(x.grad, xr.grad, 3e-2)
+  _close(res.grad, rr.grad, 1e-2)
+  _close(logits.grad, lr.grad, 5e-2)
+  _close(w1.grad, w1r.grad, 3e-2)
+  _close(b1.grad, b1r.grad, 3e-2)
+  _close(w2.grad, w2r.grad, 3e-2)
+  _close(b2.grad, b2r.grad, 3e-2)
+
+
+@pytest.mark.parametrize("kind", ["sigmoid", "softmax"])
+def test_xent(kind):
+  from vmoe_b200.ops import losses
+  torch.manual_seed(0)
+  n = 21843
+  logits = (torch.randn(16, n, device=DEV) * 3).bfloat16().requires_grad_()
+  labels = torch.zeros(16, n, device=DEV)
+  labels[torch.arange(16), torch.randint(0, n, (16,))] = 1.0
+  fn = losses.sigmoid_xent if kind == "sigmoid" else losses.softmax_xent
+  loss = fn(logits, labels)
+  w = torch.rand(16, device=DEV)
+  (loss * w).sum().backward()
+  l2 = logits.detach().float().requires_grad_()
+  if kind == "sigmoid":
+    ref = F.binary_cross_entropy_with_logits(l2, labels, reduction="none").sum(-1)
+  else:
+    ref = -(labels * F.log_softmax(l2, -1)).sum(-1)
+  (ref * w).sum().backward()
+  _close(loss, ref, 2e-3)
+  _close(logits.grad, l2.grad, 2e-2)
+
+
+@pytest.mark.parametrize("name,kw", [("adam", {}), ("sgd", {"momentum": 0.9})])
+def test_optimizer_kernel_matches_cpu(name, kw):
+  from vmoe_b200.train.optimizer import create_optimizer
+  torch.manual_seed(0)
+  shapes = [(300, 70), (5,), (64, 3, 33)]
+  ps_c = [torch.nn.Parameter(torch.randn(s)) for s in shapes]
+  ps_g = [torch.nn.Parameter(p.detach().clone().to(DEV)) for p in ps_c]
+  mk = lambda ps: create_optimizer(
+      [(f"params/p{i}/kernel", p) for i, p in enumerate(ps)], name=name, total_steps=10,
+      learning_rate=0.01, weight_decay=[("p0", 0.1)], gradient_clip={"global_norm": 1.0},
+      frozen_pattern="p1", **kw)
+  oc, og = mk(ps_c), mk(ps_g)
+  for step in range(3):
+    oc.zero_grad(); og.zero_grad()
+    for pc, pg in zip(ps_c, ps_g):
+      gr = torch.randn(pc.shape)
+      pc.grad.add_(gr); pg.grad.add_(gr.to(DEV))
+    nc, ng = oc.step(grad_div=2.0), og.step(grad_div=2.0)
+    for key in nc:
+      assert abs(float(nc[key]) - float(ng[key])) < 1e-3 * (1 + abs(float(nc[key]))), key
+  for pc, pg in zip(ps_c, ps_g):
+    _close(pg.data, pc.data, 1e-5)
+    _close(pg._bf16_shadow, pc.data, 1e-2)
+
+
+def test_graft_smoke():
+  import __graft_entry__
+  __graft_entry__.smoke()

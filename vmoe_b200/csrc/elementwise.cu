@@ -1,0 +1,357 @@
+// Memory-bound kernels of the transformer block: LayerNorm forward/backward, column sums
+// (bias gradients), NHWC image -> bf16 patch matrix. All use 16-byte vector accesses on
+// bf16 rows and fp32 arithmetic; each is one pass over its inputs.
+//
+// They replace what the reference leaves to XLA fusions (vmoe/nn/vit_moe.py:164,177,260
+// LayerNorm; :337-339 patch-embedding conv input).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx_sm100.cuh"
+#include "vmoe_api.h"
+
+namespace vmoe {
+
+void set_error(const char* fmt, const char* a, int code);
+
+static inline int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
+    return -5;
+  }
+  (void)what;
+  return 0;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z),
+         d = unpack_bf16x2(q.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 q;
+  q.x = pack_bf16x2(f[0], f[1]);
+  q.y = pack_bf16x2(f[2], f[3]);
+  q.z = pack_bf16x2(f[4], f[5]);
+  q.w = pack_bf16x2(f[6], f[7]);
+  return q;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ----------------------------------------------------------------------------- LayerNorm
+// One warp per row; lane l owns the 8-element chunks l, l+32, ... (MAXC of them at most).
+template <int MAXC>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                     const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                     float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows,
+                     int h, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int chunks = h >> 3;
+  for (long long row = warp; row < rows; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * h);
+    float v[MAXC][8];
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < chunks) {
+        unpack8(__ldg(xr + ch), v[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += v[c][i];
+      }
+    }
+    const float mean = warp_sum(s) / h;
+    float sq = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      if (lane + 32 * c < chunks) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = v[c][i] - mean;
+          sq += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / h + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * h);
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < chunks) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float t = (v[c][i] - mean) * rstd;
+          if (gamma) t *= __ldg(gamma + ch * 8 + i);
+          if (beta) t += __ldg(beta + ch * 8 + i);
+          o[i] = t;
+        }
+        yr[ch] = pack8(o);
+      }
+    }
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+  }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) with g = dy * gamma;
+// dgamma += sum_rows dy * xhat, dbeta += sum_rows dy (per-warp register partials, one atomic
+// per column and CTA at the end). `dres`, if given, is added to dx (gradient of a residual
+// branch that bypasses the norm).
+template <int MAXC>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const float* __restrict__ gamma, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+                     float* __restrict__ dbeta, long long rows, int h) {
+  extern __shared__ float red[];  // [2][h]
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int chunks = h >> 3;
+  for (int i = threadIdx.x; i < 2 * h; i += blockDim.x) red[i] = 0.f;
+  __syncthreads();
+  float ag[MAXC][8], ab[MAXC][8];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ag[c][i] = ab[c][i] = 0.f;
+  for (long long row = warp; row < rows; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * h);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * h);
+    const float mean = __ldg(mean_in + row), rstd = __ldg(rstd_in + row);
+    float xh[MAXC][8], g[MAXC][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < chunks) {
+        float xv[8], dv[8];
+        unpack8(__ldg(xr + ch), xv);
+        unpack8(__ldg(dyr + ch), dv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[c][i] = (xv[i] - mean) * rstd;
+          ag[c][i] += dv[i] * xh[c][i];
+          ab[c][i] += dv[i];
+          g[c][i] = gamma ? dv[i] * __ldg(gamma + ch * 8 + i) : dv[i];
+          s1 += g[c][i];
+          s2 += g[c][i] * xh[c][i];
+        }
+      }
+    }
+    const float m1 = warp_sum(s1) / h, m2 = warp_sum(s2) / h;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * h);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + row * h) : nullptr;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < chunks) {
+        float o[8], rv[8];
+        if (rr) unpack8(__ldg(rr + ch), rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o[i] = rstd * (g[c][i] - m1 - xh[c][i] * m2);
+          if (rr) o[i] += rv[i];
+        }
+        dxr[ch] = pack8(o);
+      }
+    }
+  }
+  if (dgamma || dbeta) {
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < chunks) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          atomicAdd(&red[ch * 8 + i], ag[c][i]);
+          atomicAdd(&red[h + ch * 8 + i], ab[c][i]);
+        }
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+      if (dgamma) atomicAdd(dgamma + i, red[i]);
+      if (dbeta) atomicAdd(dbeta + i, red[h + i]);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- column sum
+// out[b][n] += sum_r x[b][r][n]; CTA = 32 row-lanes x 32 column-chunks of 8.
+__global__ void __launch_bounds__(256)
+colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long long rows,
+              long long n, int rows_per_cta) {
+  const int b = blockIdx.z;
+  const long long chunk = static_cast<long long>(blockIdx.x) * 32 + (threadIdx.x & 31);
+  const int rlane = threadIdx.x >> 5;  // 0..7
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_cta;
+  const long long r1 = min(rows, r0 + rows_per_cta);
+  __shared__ float red[8][32][8 + 1];
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const bool ok = chunk * 8 < n;
+  if (ok) {
+    const __nv_bfloat16* base = x + (static_cast<long long>(b) * rows) * n + chunk * 8;
+    for (long long r = r0 + rlane; r < r1; r += 8) {
+      float f[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(base + r * n)), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rlane][threadIdx.x & 31][i] = acc[i];
+  __syncthreads();
+  if (rlane == 0 && ok) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += red[j][threadIdx.x & 31][i];
+      atomicAdd(out + static_cast<long long>(b) * n + chunk * 8 + i, s);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- patchify
+// images fp32/bf16 NHWC (B, H, W, C) -> bf16 (B*gh*gw, ph*pw*C); one thread per output pair.
+template <typename T>
+__global__ void __launch_bounds__(256)
+patchify_kernel(const T* __restrict__ img, __nv_bfloat16* __restrict__ out, long long total_pairs,
+                int hh, int ww, int c, int ph, int pw, int gh, int gw) {
+  const int pd = ph * pw * c;  // patch dim (even whenever pw*c is even)
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+       i < total_pairs; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * 2;
+    const int col = static_cast<int>(e % pd);
+    const long long prow = e / pd;
+    const int gx = static_cast<int>(prow % gw);
+    const int gy = static_cast<int>((prow / gw) % gh);
+    const long long b = prow / (static_cast<long long>(gw) * gh);
+    const int py = col / (pw * c);
+    const int rem = col % (pw * c);  // (px, ch) contiguous in the image row
+    const T* src = img + ((b * hh + (gy * ph + py)) * ww + gx * pw) * c + rem;
+    const float a = static_cast<float>(src[0]), bb = static_cast<float>(src[1]);
+    reinterpret_cast<uint32_t*>(out)[i] = pack_bf16x2(a, bb);
+  }
+}
+
+}  // namespace vmoe
+
+using namespace vmoe;
+
+extern "C" int vmoe_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y,
+                                  float* mean, float* rstd, int64_t rows, int64_t h, float eps,
+                                  vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows == 0) return 0;
+  if (h % 8 || h > 2048) {
+    set_error("%s (code %d)", "layernorm: hidden size must be a multiple of 8 and <= 2048", 0);
+    return -1;
+  }
+  const int threads = 256;
+  const long long blocks = (rows * 32 + threads - 1) / threads;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  auto xx = static_cast<const __nv_bfloat16*>(x);
+  auto yy = static_cast<__nv_bfloat16*>(y);
+  const int chunks = static_cast<int>(h / 8);
+#define VMOE_LN_FWD(C) layernorm_fwd_kernel<C><<<grid, threads, 0, stream>>>( \
+      xx, gamma, beta, yy, mean, rstd, rows, static_cast<int>(h), eps)
+  if (chunks <= 32 * 3) VMOE_LN_FWD(3);
+  else if (chunks <= 32 * 4) VMOE_LN_FWD(4);
+  else if (chunks <= 32 * 5) VMOE_LN_FWD(5);
+  else VMOE_LN_FWD(8);
+#undef VMOE_LN_FWD
+  return launch_status("layernorm_fwd");
+}
+
+extern "C" int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamma,
+                                  const float* mean, const float* rstd, const void* dres, void* dx,
+                                  float* dgamma, float* dbeta, int64_t rows, int64_t h,
+                                  vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows == 0) return 0;
+  if (h % 8 || h > 2048) {
+    set_error("%s (code %d)", "layernorm: hidden size must be a multiple of 8 and <= 2048", 0);
+    return -1;
+  }
+  const int threads = 256;
+  const long long blocks = (rows * 32 + threads - 1) / threads;
+  const int grid = static_cast<int>(blocks < 148 * 4 ? blocks : 148 * 4);
+  const size_t smem = 2 * h * sizeof(float);
+  auto a = static_cast<const __nv_bfloat16*>(dy);
+  auto b = static_cast<const __nv_bfloat16*>(x);
+  auto r = static_cast<const __nv_bfloat16*>(dres);
+  auto o = static_cast<__nv_bfloat16*>(dx);
+  const int chunks = static_cast<int>(h / 8);
+#define VMOE_LN_BWD(C) layernorm_bwd_kernel<C><<<grid, threads, smem, stream>>>( \
+      a, b, gamma, mean, rstd, r, o, dgamma, dbeta, rows, static_cast<int>(h))
+  if (chunks <= 32 * 3) VMOE_LN_BWD(3);
+  else if (chunks <= 32 * 4) VMOE_LN_BWD(4);
+  else if (chunks <= 32 * 5) VMOE_LN_BWD(5);
+  else VMOE_LN_BWD(8);
+#undef VMOE_LN_BWD
+  return launch_status("layernorm_bwd");
+}
+
+extern "C" int vmoe_colsum_bf16(const void* x, float* out, int64_t batch, int64_t rows, int64_t n,
+                                vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows == 0 || n == 0 || batch == 0) return 0;
+  if (n % 8) {
+    set_error("%s (code %d)", "colsum: n must be a multiple of 8", 0);
+    return -1;
+  }
+  const long long chunks = n / 8;
+  const unsigned gx = static_cast<unsigned>((chunks + 31) / 32);
+  // Enough row slices to fill the machine, at least 64 rows each.
+  long long slices = (148 * 8) / (static_cast<long long>(gx) * batch);
+  if (slices < 1) slices = 1;
+  long long rpc = (rows + slices - 1) / slices;
+  if (rpc < 64) rpc = 64;
+  const unsigned gy = static_cast<unsigned>((rows + rpc - 1) / rpc);
+  dim3 grid(gx, gy, static_cast<unsigned>(batch));
+  colsum_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), out, rows, n,
+                                          static_cast<int>(rpc));
+  return launch_status("colsum");
+}
+
+extern "C" int vmoe_patchify(const void* img, int32_t img_is_bf16, void* out, int64_t b, int64_t hh,
+                             int64_t ww, int64_t c, int64_t ph, int64_t pw, vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long gh = hh / ph, gw = ww / pw;
+  if ((pw * c) % 2) {
+    set_error("%s (code %d)", "patchify: patch_width * channels must be even", 0);
+    return -1;
+  }
+  const long long pairs = b * gh * gw * ph * pw * c / 2;
+  if (pairs == 0) return 0;
+  const int threads = 256;
+  long long blocks = (pairs + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (img_is_bf16)
+    patchify_kernel<__nv_bfloat16><<<static_cast<int>(blocks), threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(img), static_cast<__nv_bfloat16*>(out), pairs,
+        static_cast<int>(hh), static_cast<int>(ww), static_cast<int>(c), static_cast<int>(ph),
+        static_cast<int>(pw), static_cast<int>(gh), static_cast<int>(gw));
+  else
+    patchify_kernel<float><<<static_cast<int>(blocks), threads, 0, stream>>>(
+        static_cast<const float*>(img), static_cast<__nv_bfloat16*>(out), pairs,
+        static_cast<int>(hh), static_cast<int>(ww), static_cast<int>(c), static_cast<int>(ph),
+        static_cast<int>(pw), static_cast<int>(gh), static_cast<int>(gw));
+  return launch_status("patchify");
+}

@@ -53,6 +53,71 @@ typedef struct VmoeGemmArgs {
 
 VMOE_API int vmoe_gemm_bf16(const VmoeGemmArgs* args, vmoe_stream_t stream);
 
+// ----------------------------------------------------------------------------- elementwise
+// LayerNorm over the last dim of bf16 x[rows][h] (h % 8 == 0, h <= 2048); gamma/beta fp32 or
+// NULL; mean/rstd (fp32 per row) are saved for the backward pass when non-NULL.
+VMOE_API int vmoe_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y,
+                                float* mean, float* rstd, int64_t rows, int64_t h, float eps,
+                                vmoe_stream_t stream);
+// dx (bf16) = LayerNorm backward (+ dres if non-NULL); dgamma/dbeta (fp32) are accumulated.
+VMOE_API int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamma,
+                                const float* mean, const float* rstd, const void* dres, void* dx,
+                                float* dgamma, float* dbeta, int64_t rows, int64_t h,
+                                vmoe_stream_t stream);
+// out[b][n] (fp32) += sum over rows of bf16 x[b][rows][n]; n % 8 == 0.
+VMOE_API int vmoe_colsum_bf16(const void* x, float* out, int64_t batch, int64_t rows, int64_t n,
+                              vmoe_stream_t stream);
+// NHWC images (fp32 or bf16) -> bf16 patch matrix (B*gh*gw, ph*pw*C).
+VMOE_API int vmoe_patchify(const void* img, int32_t img_is_bf16, void* out, int64_t b, int64_t hh,
+                           int64_t ww, int64_t c, int64_t ph, int64_t pw, vmoe_stream_t stream);
+
+// ----------------------------------------------------------------------------- MoE routing
+// Top-K routing plan for `groups` groups of `s` items over `e` experts from softmax gates
+// (groups, s, e) fp32. Outputs: expert (groups, s, k), slot (groups, s, k) = position in the
+// expert's buffer of that group (>= capacity: dropped), slot_pair (groups, e, capacity) =
+// item * k + choice held by each buffer slot, or -1 for an empty slot.
+VMOE_API int vmoe_routing_plan(const float* gates, int32_t* expert_out, int32_t* slot_out,
+                               int32_t* slot_pair, int64_t groups, int64_t s, int64_t e, int64_t k,
+                               int64_t capacity, int32_t batch_priority, vmoe_stream_t stream);
+// Buffer row (g, e, c) at expert_base[e] + (g*C + c)*h  <-  weight * x[g, item] (zeros if the
+// slot is empty). expert_base is a device array of e addresses (local or peer memory).
+VMOE_API int vmoe_moe_gather_rows(const void* x, const int32_t* slot_pair, const float* weight,
+                                  const uint64_t* expert_base, int64_t groups, int64_t s,
+                                  int64_t e, int64_t c, int64_t k, int64_t h,
+                                  vmoe_stream_t stream);
+// out[g, item] = residual + sum_k weight_k * buffer row (expert_k, slot_k); dropped pairs skip.
+VMOE_API int vmoe_moe_combine_rows(const uint64_t* expert_base, const int32_t* expert_idx,
+                                   const int32_t* slot, const float* weight, const void* residual,
+                                   void* out, int64_t groups, int64_t s, int64_t e, int64_t c,
+                                   int64_t k, int64_t h, uint32_t* status, vmoe_stream_t stream);
+// Backward of combine: dbuf row = gate * dy[item], dgate[pair] = <dy[item], ybuf row>.
+VMOE_API int vmoe_moe_combine_bwd(const void* dy, const int32_t* slot_pair, const float* gate,
+                                  const uint64_t* ybuf_base, const uint64_t* dbuf_base,
+                                  float* dgate, int64_t groups, int64_t s, int64_t e, int64_t c,
+                                  int64_t k, int64_t h, vmoe_stream_t stream);
+
+// ----------------------------------------------------------------------------- losses
+// kind 0: sigmoid cross-entropy summed over classes; kind 1: softmax cross-entropy with soft
+// labels. logits bf16 [rows][ld] (first n columns valid), labels [rows][ld_labels] with
+// labels_dtype 0 fp32 / 1 bf16 / 2 uint8. loss fp32 [rows]; dlogits (bf16 [rows][ld], may be
+// NULL) = d loss / d logits * grad_scale.
+VMOE_API int vmoe_xent(int32_t kind, const void* logits, const void* labels, int32_t labels_dtype,
+                       float* loss, void* dlogits, int64_t rows, int64_t n, int64_t ld,
+                       int64_t ld_labels, float grad_scale, vmoe_stream_t stream);
+
+// ----------------------------------------------------------------------------- optimizer
+// Flat fp32 buffers of n elements (n % 1024 == 0); meta has one {weight_decay, lr_mult,
+// grad_scale, pad} float4 per 1024 elements. sums: double[3] = {sum g^2, sum update^2,
+// sum p_new^2}; vmoe_grad_sumsq fills sums[0] and vmoe_optimizer_step reads it for the
+// global-norm clip (clip_norm > 0) and accumulates sums[1..2]. mode 0 Adam, 1 SGD+momentum.
+VMOE_API int vmoe_grad_sumsq(const float* g, const void* meta, int64_t n, double* sums,
+                             vmoe_stream_t stream);
+VMOE_API int vmoe_optimizer_step(float* p, const float* g, float* m, float* v, void* shadow,
+                                 const void* meta, int64_t n, int32_t mode, float lr, float b1,
+                                 float b2, float eps, float bc1, float bc2, float momentum,
+                                 float clip_norm, float clip_value, float grad_div, double* sums,
+                                 vmoe_stream_t stream);
+
 // Last error text of the calling thread ("" if none).
 VMOE_API const char* vmoe_last_error(void);
 

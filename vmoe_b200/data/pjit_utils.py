@@ -1,0 +1,94 @@
+"""Host -> device input transfer with prefetch.
+
+Each process owns one GPU and its slice of the global batch, so "sharding the batch over all
+mesh axes" (``vmoe/data/pjit_utils.py:79-102``) is the identity here: the per-process batch
+goes to the local device. Batches are staged in pinned host memory and copied with
+``cudaMemcpyAsync`` on a dedicated copy stream, ``size`` batches ahead of the consumer
+(``vmoe/data/pjit_utils.py:104-115`` keeps a deque of the same depth).
+"""
+from __future__ import annotations
+
+import collections
+from typing import Any, Dict, Iterable, Iterator, Mapping, Optional
+
+import numpy as np
+import torch
+
+
+def _to_tensor(v: Any) -> torch.Tensor:
+  if isinstance(v, torch.Tensor):
+    return v
+  return torch.from_numpy(np.ascontiguousarray(v))
+
+
+class _PinnedPool:
+  """Reusable pinned staging buffers keyed by (name, shape, dtype)."""
+
+  def __init__(self, depth: int):
+    self.depth = max(1, depth)
+    self.buffers: Dict[Any, list] = {}
+    self.cursor: Dict[Any, int] = {}
+
+  def stage(self, name: str, t: torch.Tensor) -> torch.Tensor:
+    if t.is_pinned():
+      return t
+    key = (name, tuple(t.shape), t.dtype)
+    bufs = self.buffers.setdefault(key, [])
+    i = self.cursor.get(key, 0)
+    if len(bufs) < self.depth + 1:
+      bufs.append(torch.empty(t.shape, dtype=t.dtype, pin_memory=True))
+      i = len(bufs) - 1
+    buf = bufs[i % len(bufs)]
+    self.cursor[key] = (i + 1) % (self.depth + 1)
+    buf.copy_(t)
+    return buf
+
+
+def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
+                       device: Optional[torch.device] = None,
+                       dtypes: Optional[Mapping[str, torch.dtype]] = None
+                       ) -> Iterator[Dict[str, torch.Tensor]]:
+  """Yields batches whose tensors live on ``device``; ``size`` copies are kept in flight.
+
+  On a CPU-only machine (or ``device`` = cpu) batches are passed through as tensors.
+  """
+  if device is None:
+    device = (torch.device("cuda", torch.cuda.current_device())
+              if torch.cuda.is_available() else torch.device("cpu"))
+  device = torch.device(device)
+  if device.type != "cuda":
+    for batch in iterator:
+      yield {k: _to_tensor(v) for k, v in batch.items()}
+    return
+  stream = torch.cuda.Stream(device=device)
+  pool = _PinnedPool(size)
+  queue: collections.deque = collections.deque()
+
+  def enqueue(batch):
+    out = {}
+    with torch.cuda.stream(stream):
+      for k, v in batch.items():
+        t = pool.stage(k, _to_tensor(v))
+        d = t.to(device, non_blocking=True)
+        if dtypes and k in dtypes:
+          d = d.to(dtypes[k])
+        out[k] = d
+      ev = torch.cuda.Event()
+      ev.record(stream)
+    queue.append((out, ev))
+
+  it = iter(iterator)
+  exhausted = False
+  while True:
+    while not exhausted and len(queue) < max(1, size):
+      try:
+        enqueue(next(it))
+      except StopIteration:
+        exhausted = True
+    if not queue:
+      return
+    out, ev = queue.popleft()
+    torch.cuda.current_stream(device).wait_event(ev)
+    for t in out.values():
+      t.record_stream(torch.cuda.current_stream(device))
+    yield out

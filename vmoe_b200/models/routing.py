@@ -16,6 +16,7 @@ import torch
 from torch import nn
 
 from vmoe_b200 import moe
+from vmoe_b200 import ops
 from vmoe_b200.parallel.exchange import ExpertExchange, LOCAL_EXCHANGE
 
 Tensor = torch.Tensor
@@ -136,6 +137,18 @@ class NoisyTopExpertsPerItemRouter(_RouterBase):
   def _create_dispatcher(self, gates: Tensor, inputs: Optional[Tensor] = None):
     kwargs = dict(self.dispatcher_kwargs)
     use_bf16 = kwargs.pop("bfloat16", False)
+    if (inputs is not None and inputs.is_cuda and inputs.dtype == torch.bfloat16 and
+        ops.cuda_kernels_enabled() and kwargs.get("name") in ("einsum", "indices")):
+      # GPU path: one routing-plan kernel, indices form (identical semantics for both names).
+      from vmoe_b200.ops import moe_ops
+      g, s, e = gates.shape
+      capacity = moe._resolve_capacity(
+          kwargs.get("capacity"), kwargs.get("capacity_factor"),
+          s * self.num_selected_experts, e, kwargs.get("capacity_ceil_or_round", "ceil"),
+          kwargs.get("capacity_multiple_of", 4))
+      return moe_ops.FusedTopKDispatcher(gates, self.num_selected_experts, capacity,
+                                         bool(kwargs.get("batch_priority", False)),
+                                         exchange=self.exchange)
     d = moe.get_top_experts_per_item_dispatcher(
         gates, num_selected_experts=self.num_selected_experts, exchange=self.exchange, **kwargs)
     return moe.Bfloat16Dispatcher(d) if use_bf16 else d

@@ -106,6 +106,8 @@ class DenseEinsumDispatcher(BaseDispatcher):
   """Every item goes to every expert (C = S); ``combine_weights`` is ``(G, S, E)``."""
   combine_weights: Tensor
   exchange: ExpertExchange = LOCAL_EXCHANGE
+  partition_spec: Any = None      # accepted for config compatibility; placement is explicit
+  einsum_precision: Any = None
 
   def dispatch(self, data: Tensor) -> Tensor:
     g, s, e = self.combine_weights.shape
@@ -130,6 +132,8 @@ class EinsumDispatcher(BaseDispatcher):
   combine_weights: Tensor
   dispatch_weights: Optional[Tensor] = None
   exchange: ExpertExchange = LOCAL_EXCHANGE
+  partition_spec: Any = None
+  einsum_precision: Any = None
 
   def _dispatch_w(self) -> Tensor:
     return self.combine_weights > 0 if self.dispatch_weights is None else self.dispatch_weights
@@ -162,6 +166,8 @@ class ExpertIndicesDispatcher(BaseDispatcher):
   num_experts: int
   capacity: int
   exchange: ExpertExchange = LOCAL_EXCHANGE
+  partition_spec: Any = None
+  einsum_precision: Any = None
 
   def _flat_index(self) -> Tuple[Tensor, Tensor]:
     e, p = self.indices[..., 0].long(), self.indices[..., 1].long()

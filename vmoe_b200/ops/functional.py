@@ -67,13 +67,19 @@ class _LinearFn(torch.autograd.Function):
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
       x2 = x2.contiguous()
-    need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    need_grad = any(ctx.needs_input_grad)
     n = weight.shape[0]
     pre = None
     if act == ACT_GELU and need_grad:
       pre = torch.empty(x2.shape[0], n, dtype=torch.bfloat16, device=x.device)
     res2 = residual.reshape(-1, n) if residual is not None else None
-    y = gemm(x2, w16, bias=bias, act=act, residual=res2, out_pre=pre)
+    out = None
+    if n % 8:
+      # Rows are padded to a 16-byte multiple so the backward GEMMs can read dy through TMA;
+      # the caller sees the (rows, n) view.
+      n_pad = (n + 7) // 8 * 8
+      out = torch.empty(x2.shape[0], n_pad, dtype=torch.bfloat16, device=x.device)[:, :n]
+    y = gemm(x2, w16, bias=bias, act=act, residual=res2, out_pre=pre, out=out)
     ctx.save_for_backward(x2, weight, pre)
     ctx.has_bias = bias is not None
     ctx.has_res = residual is not None
@@ -86,15 +92,18 @@ class _LinearFn(torch.autograd.Function):
     w16 = bf16_shadow(weight)
     n, k = weight.shape
     dy2 = dy.reshape(-1, n)
-    if not dy2.is_contiguous():
-      dy2 = dy2.contiguous()
+    if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+      n_pad = (n + 7) // 8 * 8
+      padded = torch.zeros(dy2.shape[0], n_pad, dtype=dy2.dtype, device=dy2.device)
+      padded[:, :n].copy_(dy2)
+      dy2 = padded[:, :n]
     d_res = dy if ctx.has_res else None
     if pre is not None:
       # Stand-alone GELU linear layers are off the hot path (the MLP blocks use expert_mlp,
       # whose dgrad GEMM applies gelu' in its epilogue).
       from vmoe_b200.ops.gemm import gelu_tanh_grad
       dy2 = (dy2.float() * gelu_tanh_grad(pre.float())).to(torch.bfloat16)
-    dbias = reduce.colsum(dy2) if ctx.has_bias else None
+    dbias = reduce.colsum(dy2) if ctx.has_bias else None  # handles padded rows
     dx = None
     if ctx.needs_input_grad[0]:
       dx = gemm(dy2, w16, b_mn_major=True).reshape(ctx.x_shape)
@@ -139,7 +148,7 @@ class _ExpertMlpFn(torch.autograd.Function):
     e, r, h = x.shape
     m = w1.shape[1]
     x = x.contiguous()
-    need_grad = torch.is_grad_enabled()
+    need_grad = any(ctx.needs_input_grad)
     pre = torch.empty(e, r, m, dtype=torch.bfloat16, device=x.device) if need_grad else None
     hid = gemm(x, w1h, bias=b1, act=ACT_GELU, out_pre=pre)
     y = gemm(hid, w2h, bias=b2, residual=residual)
@@ -196,11 +205,10 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               dropout_p: float = 0.0, training: bool = False) -> torch.Tensor:
   """Non-causal softmax attention; ``q: (B, Tq, heads, d)``, ``k, v: (B, Tk, heads, d)``."""
   d = q.shape[-1]
-  if (_fast(q) and not (training and dropout_p > 0) and d in (64, 80, 128)
-      and q.shape[1] == k.shape[1]):
-    from vmoe_b200.ops import attention as attn_ops
-    if attn_ops.supported(q, k, v):
-      return attn_ops.attention(q, k, v)
+  if _fast(q) and not (training and dropout_p > 0):
+    from vmoe_b200.ops import attention_ops
+    if attention_ops.supported(q, k, v):
+      return attention_ops.attention(q, k, v)
   scale = 1.0 / math.sqrt(d)
   logits = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
   probs = torch.softmax(logits.float(), dim=-1).to(q.dtype)
