@@ -165,3 +165,22 @@ def test_optimizer_kernel_matches_cpu(name, kw):
 def test_graft_smoke():
   import __graft_entry__
   __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("b,t,h", [(2, 197, 3), (3, 50, 2), (1, 256, 2), (2, 129, 1), (2, 16, 1)])
+def test_packed_attention(b, t, h):
+  from vmoe_b200.ops import attention_ops
+  torch.manual_seed(0)
+  qkv = torch.randn(b, t, 3, h, 64, device=DEV).bfloat16().requires_grad_()
+  out = attention_ops.packed_attention(qkv)
+  dout = torch.randn_like(out)
+  out.backward(dout)
+  ref_in = qkv.detach().float().requires_grad_()
+  q, k, v = ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2]
+  logits = torch.einsum("bqhd,bkhd->bhqk", q, k) / 8.0
+  ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(logits, -1), v)
+  ref.backward(dout.float())
+  _close(out, ref, 2e-2)
+  _close(qkv.grad[:, :, 2], ref_in.grad[:, :, 2], 3e-2)  # dV
+  _close(qkv.grad[:, :, 1], ref_in.grad[:, :, 1], 3e-2)  # dK
+  _close(qkv.grad[:, :, 0], ref_in.grad[:, :, 0], 3e-2)  # dQ

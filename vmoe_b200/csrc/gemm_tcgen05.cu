@@ -2,8 +2,10 @@
 // tcgen05.mma (UMMA 128x256x16, fp32 accumulators in TMEM, double-buffered) -> tcgen05.ld
 // epilogue with bias / GELU / GELU-grad / residual / column-sum / bf16|fp32|atomic stores.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. 32*(w%4)+31).
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4) .. 32*(w%4)+31 and half of the
+// tile's columns). bf16 outputs leave through 64B-swizzled shared-memory staging and TMA
+// stores, which clip rows and columns that fall outside the matrix.
 //
 // This one kernel covers every dense and expert matmul of the model: forward (x W^T), dgrad
 // (dy W, B read MN-major) and wgrad (dy^T x, both operands MN-major, split-K with fp32
@@ -17,6 +19,7 @@
 #include <string.h>
 
 #include "ptx_sm100.cuh"
+#include "tma_host.h"
 #include "vmoe_api.h"
 
 namespace vmoe {
@@ -30,8 +33,12 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int CHUNK_BYTES = 64 * BK * 2;    // one 64 x 64 MN-major box = 8 KiB
 constexpr int TMEM_COLS = 512;              // two 128 x 256 fp32 accumulators
-constexpr int GEMM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256;
+constexpr int EPI_WARPS = 8;                // two per TMEM lane quadrant, 128 columns each
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_CHUNK_BYTES = 32 * 32 * 2;  // 32 rows x 32 bf16 columns, 64 B swizzled rows
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * 2 * EPI_CHUNK_BYTES;  // C and C2 staging per warp
+constexpr int SMEM_BYTES =
+    STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_STAGE_BYTES + 1024 /*align*/ + 256;
 
 struct GemmParams {
   void* C;
@@ -48,6 +55,9 @@ struct GemmParams {
   int a_mn_major, b_mn_major;
   int c_fp32, c_atomic, act, split_k;
   unsigned a_ready_epoch;
+  int tma_store;  // bf16 outputs go through smem staging + TMA stores
+  int c2_gelu_grad;  // C2 receives gelu'(pre-activation) instead of the pre-activation
+  int pre_is_grad;   // gelu_pre already holds gelu'(x): plain multiply
 };
 
 struct TileCoord {
@@ -90,13 +100,15 @@ __device__ __forceinline__ void warp_transpose_reduce(float (&v)[32], int lane) 
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_c2,
                  const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* sEpi = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_STAGE_BYTES);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -117,11 +129,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, 4);  // one arrival per epilogue warp
+      mbar_init(bar_tempty + 8 * s, EPI_WARPS);  // one arrival per epilogue warp
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.tma_store) {
+      tma_prefetch_desc(&tma_c);
+      if (p.C2) tma_prefetch_desc(&tma_c2);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -257,7 +273,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int quad = warp & 3;         // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which 128 columns of the tile this warp handles
+    uint8_t* stage_c = sEpi + (warp - 2) * 2 * EPI_CHUNK_BYTES;
+    uint8_t* stage_c2 = stage_c + EPI_CHUNK_BYTES;
+    // 64B-swizzled position of this lane's row inside a 32 x 32 bf16 staging tile.
+    const uint32_t st_row = static_cast<uint32_t>(lane) * 64u;
+    const uint32_t st_xor = (static_cast<uint32_t>(lane) >> 1) & 3u;
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
@@ -274,7 +296,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_after();
       const bool empty_k = kt0 >= kt1;  // a split with no K tiles contributes nothing
-      const int row = t.mt * BM + quad * 32 + lane;
+      const int row0 = t.mt * BM + quad * 32;
+      const int row = row0 + lane;
       const bool row_ok = row < p.M;
       const int n0 = t.nt * BN;
       const long long crow = static_cast<long long>(t.b) * p.c_batch_stride +
@@ -283,10 +306,56 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                  : nullptr;
       // Only the first split adds bias/residual so that atomically summed splits count them once.
       const bool first_split = t.ks == 0;
+      // Epilogue input tile (gelu_pre or residual): fetched one chunk ahead with coalesced
+      // 16-byte loads (8 rows x 64 B per instruction), then re-distributed to one row per lane
+      // through the (otherwise unused) second staging tile.
+      const __nv_bfloat16* in_ptr = nullptr;
+      long long in_ld = 0;
+      if (!p.C2 && !(p.gelu_pre && p.residual)) {
+        if (p.gelu_pre) {
+          in_ptr = p.gelu_pre;
+          in_ld = p.ldr2;
+        } else if (p.residual && first_split) {
+          in_ptr = p.residual;
+          in_ld = p.ldr;
+        }
+        if (in_ld % 8 || p.N % 8) in_ptr = nullptr;
+      }
+      const int pf_r = lane >> 2, pf_c = lane & 3;
+      uint4 pf[4];
+      auto prefetch_input = [&](int cc) {
+        const int colp = n0 + cc * 32 + pf_c * 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rw = row0 + pf_r + 8 * i;
+          pf[i] = make_uint4(0, 0, 0, 0);
+          if (rw < p.M && colp + 8 <= p.N)
+            pf[i] = __ldg(reinterpret_cast<const uint4*>(
+                in_ptr + static_cast<long long>(t.b) * p.r_batch_stride +
+                static_cast<long long>(rw) * in_ld + colp));
+        }
+      };
+      if (in_ptr && n0 + half * 128 < p.N) prefetch_input(half * 4);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * 4; c < half * 4 + 4; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;
+        uint4 in_row[4];
+        if (in_ptr) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t rr = static_cast<uint32_t>(pf_r + 8 * i);
+            *reinterpret_cast<uint4*>(stage_c2 + rr * 64u +
+                                      ((static_cast<uint32_t>(pf_c) ^ ((rr >> 1) & 3u)) << 4)) = pf[i];
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            in_row[i] = *reinterpret_cast<const uint4*>(
+                stage_c2 + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4));
+          __syncwarp();
+          if (c + 1 < half * 4 + 4 && col0 + 32 < p.N) prefetch_input(c + 1);
+        }
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + slot * BN + c * 32,
                       r);
@@ -296,14 +365,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.0f : __uint_as_float(r[i]);
         const bool full_cols = col0 + 32 <= p.N;
         if (bias && first_split) {
+          if (full_cols) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (full_cols || col0 + i < p.N) v[i] += __ldg(bias + col0 + i);
+            for (int i = 0; i < 8; ++i) {
+              const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + col0) + i);
+              v[4 * i + 0] += b4.x;
+              v[4 * i + 1] += b4.y;
+              v[4 * i + 2] += b4.z;
+              v[4 * i + 3] += b4.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __ldg(bias + col0 + i);
+          }
+        }
+        if (p.tma_store) {
+          // The staging tiles are reused every chunk: wait until the TMA engine has read the
+          // previous contents.
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
         }
         const bool vec_bf16 = full_cols && (p.ldc % 8 == 0);
-        if (p.C2 && row_ok) {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0;
-          if (vec_bf16) {
+        if (p.C2 && p.c2_gelu_grad) {
+          // Fused forward: C = gelu(v) and C2 = gelu'(v) share one tanh.
+          float a[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = v[i];
+            const float x2 = x * x;
+            const float tt = tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x2));
+            const float hp = 0.5f * (1.0f + tt);
+            a[i] = x * hp;
+            v[i] = hp + 0.5f * x * (1.0f - tt * tt) * (0.7978845608028654f * (1.0f + 0.134145f * x2));
+          }
+          // v now holds gelu' (stored to C2 below); a holds the activation (restored after).
+          if (p.tma_store) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 q;
@@ -311,49 +408,99 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
               q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
               q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-              reinterpret_cast<uint4*>(out)[i] = q;
+              *reinterpret_cast<uint4*>(stage_c2 + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
             }
-          } else {
+          } else if (row_ok) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (col0 + i < p.N) out[i] = __float2bfloat16(v[i]);
           }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = a[i];
+        } else if (p.C2) {
+          if (p.tma_store) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 q;
+              q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+              q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+              q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+              q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+              *reinterpret_cast<uint4*>(stage_c2 + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
+            }
+          } else if (row_ok) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0;
+            if (vec_bf16) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 q;
+                q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+                q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+                reinterpret_cast<uint4*>(out)[i] = q;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) out[i] = __float2bfloat16(v[i]);
+            }
+          }
         }
-        if (p.act == 1) {
+        if (p.act == 1 && !(p.C2 && p.c2_gelu_grad)) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
         }
         if (p.gelu_pre && row_ok) {
           const __nv_bfloat16* pre = p.gelu_pre + static_cast<long long>(t.b) * p.r_batch_stride +
                                      static_cast<long long>(row) * p.ldr2 + col0;
-          if (full_cols && (p.ldr2 % 8 == 0)) {
+          if (in_ptr == p.gelu_pre || (full_cols && (p.ldr2 % 8 == 0))) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 q = __ldg(reinterpret_cast<const uint4*>(pre) + i);
+              const uint4 q = (in_ptr == p.gelu_pre)
+                                  ? in_row[i]
+                                  : __ldg(reinterpret_cast<const uint4*>(pre) + i);
               const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y);
               const float2 f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
-              v[8 * i + 0] *= gelu_tanh_grad(f0.x);
-              v[8 * i + 1] *= gelu_tanh_grad(f0.y);
-              v[8 * i + 2] *= gelu_tanh_grad(f1.x);
-              v[8 * i + 3] *= gelu_tanh_grad(f1.y);
-              v[8 * i + 4] *= gelu_tanh_grad(f2.x);
-              v[8 * i + 5] *= gelu_tanh_grad(f2.y);
-              v[8 * i + 6] *= gelu_tanh_grad(f3.x);
-              v[8 * i + 7] *= gelu_tanh_grad(f3.y);
+              if (p.pre_is_grad) {
+                v[8 * i + 0] *= f0.x;
+                v[8 * i + 1] *= f0.y;
+                v[8 * i + 2] *= f1.x;
+                v[8 * i + 3] *= f1.y;
+                v[8 * i + 4] *= f2.x;
+                v[8 * i + 5] *= f2.y;
+                v[8 * i + 6] *= f3.x;
+                v[8 * i + 7] *= f3.y;
+              } else {
+                v[8 * i + 0] *= gelu_tanh_grad(f0.x);
+                v[8 * i + 1] *= gelu_tanh_grad(f0.y);
+                v[8 * i + 2] *= gelu_tanh_grad(f1.x);
+                v[8 * i + 3] *= gelu_tanh_grad(f1.y);
+                v[8 * i + 4] *= gelu_tanh_grad(f2.x);
+                v[8 * i + 5] *= gelu_tanh_grad(f2.y);
+                v[8 * i + 6] *= gelu_tanh_grad(f3.x);
+                v[8 * i + 7] *= gelu_tanh_grad(f3.y);
+              }
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] *= gelu_tanh_grad(__bfloat162float(pre[i]));
+              if (col0 + i < p.N) {
+                const float pv = __bfloat162float(pre[i]);
+                v[i] *= p.pre_is_grad ? pv : gelu_tanh_grad(pv);
+              }
           }
         }
         if (p.residual && row_ok && first_split) {
           const __nv_bfloat16* res = p.residual + static_cast<long long>(t.b) * p.r_batch_stride +
                                      static_cast<long long>(row) * p.ldr + col0;
-          if (full_cols && (p.ldr % 8 == 0)) {
+          if (in_ptr == p.residual || (full_cols && (p.ldr % 8 == 0))) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 q = __ldg(reinterpret_cast<const uint4*>(res) + i);
+              const uint4 q = (in_ptr == p.residual)
+                                  ? in_row[i]
+                                  : __ldg(reinterpret_cast<const uint4*>(res) + i);
               const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y);
               const float2 f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
               v[8 * i + 0] += f0.x;
@@ -371,7 +518,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + i < p.N) v[i] += __bfloat162float(res[i]);
           }
         }
-        if (row_ok) {
+        if (p.tma_store) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+            q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+            q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+            q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+            *reinterpret_cast<uint4*>(stage_c + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
+          }
+          fence_proxy_async();  // make the staged tile visible to the TMA engine
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tma_c, smem_u32(stage_c), col0, row0, t.b);
+            if (p.C2) tma_store_3d(&tma_c2, smem_u32(stage_c2), col0, row0, t.b);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        } else if (row_ok) {
           if (!p.c_fp32) {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
             if (vec_bf16) {
@@ -422,6 +586,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
     }
+    // Outstanding TMA stores must finish reading shared memory before the CTA exits.
+    if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tc_fence_before();
@@ -439,33 +605,17 @@ void set_error(const char* fmt, const char* a, int code) {
   snprintf(g_err, sizeof(g_err), fmt, a, code);
 }
 
-static PFN_cuTensorMapEncodeTiled get_encode_fn() {
-  static PFN_cuTensorMapEncodeTiled fn = nullptr;
-  if (fn) return fn;
-  void* ptr = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
-  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || ptr == nullptr) return nullptr;
-  fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(ptr);
-  return fn;
-}
-
 // bf16 matrix stored [batch][rows][ld] viewed as a 3-D tensor (inner, rows, batch) with a
 // 64-element (128 B) swizzled inner box.
 int make_bf16_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch,
-                  uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_rows) {
-  PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
-  if (!enc) {
-    set_error("%s (code %d)", "cuTensorMapEncodeTiled entry point not available", 0);
-    return -2;
-  }
+                  uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t box_rows,
+                  uint32_t box_inner = 64, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   cuuint64_t dims[3] = {inner, rows, batch};
   cuuint64_t strides[2] = {ld_elems * 2, (batch > 1 ? batch_stride_elems : rows * ld_elems) * 2};
-  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = tma_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr),
+                                dims, strides, box, estr, swizzle);
   if (r != CUDA_SUCCESS) {
     set_error("%s (code %d)", "cuTensorMapEncodeTiled failed", static_cast<int>(r));
     return -3;
@@ -505,8 +655,26 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     rc = make_bf16_map(&mb, a->B, a->N, a->K, a->batch, a->ldb, a->b_batch_stride, BK);
   if (rc) return rc;
 
+  // bf16 outputs: 32 x 32 boxes with 64B swizzle, written by TMA from the epilogue staging.
+  CUtensorMap mc, mc2;
+  memset(&mc, 0, sizeof(mc));
+  memset(&mc2, 0, sizeof(mc2));
+  const bool tma_store = !a->c_fp32 && (a->ldc % 8 == 0) && (a->c_batch_stride % 8 == 0) &&
+                         !(reinterpret_cast<uintptr_t>(a->C) & 15) &&
+                         (a->C2 == nullptr || !(reinterpret_cast<uintptr_t>(a->C2) & 15));
+  if (tma_store) {
+    rc = make_bf16_map(&mc, a->C, a->N, a->M, a->batch, a->ldc, a->c_batch_stride, 32, 32,
+                       CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    if (a->C2) {
+      rc = make_bf16_map(&mc2, a->C2, a->N, a->M, a->batch, a->ldc, a->c_batch_stride, 32, 32,
+                         CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+    }
+  }
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.tma_store = tma_store ? 1 : 0;
   p.C = a->C;
   p.C2 = a->C2;
   p.bias = a->bias;
@@ -532,6 +700,8 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   p.act = a->act;
   p.split_k = a->split_k > 1 ? a->split_k : 1;
   p.a_ready_epoch = a->a_ready_epoch;
+  p.c2_gelu_grad = a->c2_gelu_grad;
+  p.pre_is_grad = a->pre_is_grad;
 
   static int sm_count = 0;
   static bool attr_set = false;
@@ -551,7 +721,7 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   const long long tiles = a->batch * num_m * num_n * p.split_k;
   int max_ctas = a->num_sms > 0 ? a->num_sms : sm_count;
   int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
-  gemm_bf16_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+  gemm_bf16_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));

@@ -107,6 +107,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* desc, uint
       : "memory");
 }
 
+// 3-D tiled store shared -> global (bulk async group; rows/columns outside the tensor are clipped).
+__device__ __forceinline__ void tma_store_3d(const void* desc, uint32_t src, int c0, int c1,
+                                             int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(desc)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
 // ----------------------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),

@@ -22,7 +22,8 @@ typedef void* vmoe_stream_t;  // cudaStream_t
 //
 // Epilogue, in this order, per output element v = acc:
 //   v += bias[col]                       (bias != NULL; fp32, length N per batch)
-//   pre-activation copy to C2            (C2 != NULL; bf16, same layout as C)
+//   pre-activation copy to C2            (C2 != NULL; bf16, same layout as C; or gelu'(v)
+//                                         when c2_gelu_grad is set, for a cheaper backward)
 //   v = gelu_tanh(v)                     (act == 1)
 //   v *= gelu_tanh'(gelu_pre[row, col])  (gelu_pre != NULL; bf16, leading dim ldr2)
 //   v += residual[row, col]              (residual != NULL; bf16, leading dim ldr)
@@ -49,6 +50,8 @@ typedef struct VmoeGemmArgs {
   int32_t split_k;   // >1 splits the K range over CTAs (needs c_atomic)
   uint32_t a_ready_epoch;  // A tile (b, mt) may be loaded once a_ready[...] >= epoch * rows
   int32_t num_sms;   // CTAs to launch at most (0: all SMs of the device)
+  int32_t c2_gelu_grad;  // with act == 1: C2 receives gelu'(v) instead of v
+  int32_t pre_is_grad;   // gelu_pre already holds gelu'(x): multiply by it as is
 } VmoeGemmArgs;
 
 VMOE_API int vmoe_gemm_bf16(const VmoeGemmArgs* args, vmoe_stream_t stream);
@@ -117,6 +120,30 @@ VMOE_API int vmoe_optimizer_step(float* p, const float* g, float* m, float* v, v
                                  float b2, float eps, float bc1, float bc2, float momentum,
                                  float clip_norm, float clip_value, float grad_div, double* sums,
                                  vmoe_stream_t stream);
+
+// ----------------------------------------------------------------------------- attention
+// Non-causal softmax attention, head dim 64, 1 <= T <= 256, bf16. q/k/v/dq/dk/dv and
+// out/d_out are addressed as ptr + b*batch + t*tok + h*head (+ d), strides in elements and
+// multiples of 8, so q, k and v may point into one packed (B, T, 3, H, 64) projection output.
+typedef struct VmoeAttnArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;          // forward output (input of the backward pass)
+  float* lse;         // (B, H, T) log-sum-exp of the scaled scores
+  const void* d_out;  // backward only
+  void* dq;
+  void* dk;
+  void* dv;
+  unsigned* status;
+  int64_t B, H, T, D;
+  int64_t q_tok, q_head, q_batch;  // strides of q, k and v
+  int64_t o_tok, o_head, o_batch;  // strides of out and d_out
+  int64_t g_tok, g_head, g_batch;  // strides of dq, dk and dv
+  float scale;                     // usually 1 / sqrt(D)
+} VmoeAttnArgs;
+VMOE_API int vmoe_attention_fwd(const VmoeAttnArgs* args, vmoe_stream_t stream);
+VMOE_API int vmoe_attention_bwd(const VmoeAttnArgs* args, vmoe_stream_t stream);
 
 // Last error text of the calling thread ("" if none).
 VMOE_API const char* vmoe_last_error(void);

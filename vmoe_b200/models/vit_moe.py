@@ -235,6 +235,9 @@ class MultiHeadDotProductAttention(nn.Module):
     h, d = self.num_heads, self.head_dim
     if inputs_kv is None or inputs_kv is inputs_q:
       qkv = self.qkv(inputs_q).reshape(b, tq, 3, h, d)
+      if self.query_ln is None:
+        a = ops.attention_packed(qkv, dropout_p=self.dropout_rate, training=self.training)
+        return self.out(a.reshape(b, tq, h * d), residual=residual)
       q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
     else:
       w, bias = self.qkv.weight, self.qkv.bias

@@ -57,6 +57,37 @@ def bf16_shadow(p: torch.Tensor) -> torch.Tensor:
   return sh
 
 
+def _grad_target(p: torch.Tensor):
+  """The fp32 gradient buffer of a parameter if one is bound (flat optimizer buffers), so the
+  weight-gradient GEMM can accumulate into it in place instead of going through autograd's
+  allocate + add."""
+  g = getattr(p, "grad", None)
+  if (g is not None and g.dtype == torch.float32 and g.shape == p.shape and g.is_contiguous()
+      and not g.requires_grad):
+    return g
+  return None
+
+
+def wgrad(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, split_k: int = 1):
+  """dW = dy^T x for ``weight`` (.., N, K); returns None if accumulated into ``weight.grad``."""
+  tgt = _grad_target(weight)
+  if tgt is not None:
+    gemm(dy, x, a_mn_major=True, b_mn_major=True, out=tgt, accumulate=True, split_k=split_k)
+    return None
+  dw = torch.zeros(weight.shape, dtype=torch.float32, device=dy.device)
+  gemm(dy, x, a_mn_major=True, b_mn_major=True, out=dw, accumulate=True, split_k=split_k)
+  return dw
+
+
+def bias_grad(dy: torch.Tensor, bias: torch.Tensor):
+  """Column sums of ``dy`` for ``bias``; None if accumulated into ``bias.grad``."""
+  tgt = _grad_target(bias)
+  if tgt is not None:
+    reduce.colsum(dy, out=tgt)
+    return None
+  return reduce.colsum(dy)
+
+
 # ----------------------------------------------------------------------------------- linear
 class _LinearFn(torch.autograd.Function):
   """y = act(x W^T + b) (+ residual) on the tcgen05 GEMM; backward = dgrad + wgrad GEMMs."""
@@ -82,6 +113,7 @@ class _LinearFn(torch.autograd.Function):
     y = gemm(x2, w16, bias=bias, act=act, residual=res2, out_pre=pre, out=out)
     ctx.save_for_backward(x2, weight, pre)
     ctx.has_bias = bias is not None
+    ctx.bias = bias
     ctx.has_res = residual is not None
     ctx.x_shape = x.shape
     return y.reshape(*x.shape[:-1], n)
@@ -103,16 +135,13 @@ class _LinearFn(torch.autograd.Function):
       # whose dgrad GEMM applies gelu' in its epilogue).
       from vmoe_b200.ops.gemm import gelu_tanh_grad
       dy2 = (dy2.float() * gelu_tanh_grad(pre.float())).to(torch.bfloat16)
-    dbias = reduce.colsum(dy2) if ctx.has_bias else None  # handles padded rows
+    dbias = bias_grad(dy2, ctx.bias) if ctx.has_bias else None  # handles padded rows
     dx = None
     if ctx.needs_input_grad[0]:
       dx = gemm(dy2, w16, b_mn_major=True).reshape(ctx.x_shape)
     dw = None
     if ctx.needs_input_grad[1]:
-      dw = torch.zeros(n, k, dtype=torch.float32, device=dy.device)
-      m = dy2.shape[0]
-      gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=dw, accumulate=True,
-           split_k=_wgrad_split(n, k, m))
+      dw = wgrad(dy2, x2, weight, split_k=_wgrad_split(n, k, dy2.shape[0]))
     return dx, dw, dbias, d_res, None
 
 
@@ -150,9 +179,10 @@ class _ExpertMlpFn(torch.autograd.Function):
     x = x.contiguous()
     need_grad = any(ctx.needs_input_grad)
     pre = torch.empty(e, r, m, dtype=torch.bfloat16, device=x.device) if need_grad else None
-    hid = gemm(x, w1h, bias=b1, act=ACT_GELU, out_pre=pre)
+    hid = gemm(x, w1h, bias=b1, act=ACT_GELU, out_pre=pre, out_pre_is_grad=True)
     y = gemm(hid, w2h, bias=b2, residual=residual)
     ctx.save_for_backward(x, w1, w2, pre, hid)
+    ctx.biases = (b1, b2)
     ctx.has_res = residual is not None
     return y
 
@@ -163,13 +193,15 @@ class _ExpertMlpFn(torch.autograd.Function):
     e, r, h = x.shape
     m = w1.shape[1]
     dy = dy.contiguous()
-    db2 = reduce.colsum(dy)
-    dw2 = torch.zeros(e, h, m, dtype=torch.float32, device=dy.device)
-    gemm(dy, hid, a_mn_major=True, b_mn_major=True, out=dw2, accumulate=True)
-    db1 = torch.zeros(e, m, dtype=torch.float32, device=dy.device)
-    dpre = gemm(dy, w2h, b_mn_major=True, gelu_pre=pre, colsum=db1)
-    dw1 = torch.zeros(e, m, h, dtype=torch.float32, device=dy.device)
-    gemm(dpre, x, a_mn_major=True, b_mn_major=True, out=dw1, accumulate=True)
+    b1, b2 = ctx.biases
+    db2 = bias_grad(dy, b2)
+    dw2 = wgrad(dy, hid, w2, split_k=_wgrad_split(h, m, r) if e == 1 else 1)
+    tgt = _grad_target(b1)
+    db1 = tgt if tgt is not None else torch.zeros(e, m, dtype=torch.float32, device=dy.device)
+    dpre = gemm(dy, w2h, b_mn_major=True, gelu_pre=pre, gelu_pre_is_grad=True, colsum=db1)
+    if tgt is not None:
+      db1 = None
+    dw1 = wgrad(dpre, x, w1, split_k=_wgrad_split(m, h, r) if e == 1 else 1)
     dx = gemm(dpre, w1h, b_mn_major=True) if ctx.needs_input_grad[0] else None
     return dx, dw1, db1, dw2, db2, (dy if ctx.has_res else None)
 
@@ -205,13 +237,18 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               dropout_p: float = 0.0, training: bool = False) -> torch.Tensor:
   """Non-causal softmax attention; ``q: (B, Tq, heads, d)``, ``k, v: (B, Tk, heads, d)``."""
   d = q.shape[-1]
-  if _fast(q) and not (training and dropout_p > 0):
-    from vmoe_b200.ops import attention_ops
-    if attention_ops.supported(q, k, v):
-      return attention_ops.attention(q, k, v)
   scale = 1.0 / math.sqrt(d)
   logits = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
   probs = torch.softmax(logits.float(), dim=-1).to(q.dtype)
   if training and dropout_p > 0:
     probs = F.dropout(probs, dropout_p, True)
   return torch.einsum("bhqk,bkhd->bqhd", probs, v)
+
+
+def attention_packed(qkv: torch.Tensor, dropout_p: float = 0.0, training: bool = False):
+  """Self-attention on the packed QKV projection ``(B, T, 3, H, D)`` -> ``(B, T, H, D)``."""
+  if _fast(qkv) and not (training and dropout_p > 0):
+    from vmoe_b200.ops import attention_ops
+    if attention_ops.packed_supported(qkv):
+      return attention_ops.packed_attention(qkv)
+  return attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], dropout_p, training)

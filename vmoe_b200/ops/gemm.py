@@ -34,7 +34,8 @@ def _as3d(t: torch.Tensor) -> torch.Tensor:
 
 def gemm_reference(a, b, *, a_mn_major=False, b_mn_major=False, bias=None, act=ACT_NONE,
                    residual=None, gelu_pre=None, out=None, out_pre=None, colsum=None,
-                   out_dtype=torch.bfloat16, accumulate=False):
+                   out_dtype=torch.bfloat16, accumulate=False, out_pre_is_grad=False,
+                   gelu_pre_is_grad=False):
   """fp32 PyTorch evaluation of the kernel's contract (any device)."""
   a3, b3 = _as3d(a).float(), _as3d(b).float()
   if a_mn_major:
@@ -45,11 +46,13 @@ def gemm_reference(a, b, *, a_mn_major=False, b_mn_major=False, bias=None, act=A
   if bias is not None:
     v = v + bias.float().reshape(v.shape[0], 1, -1)
   if out_pre is not None:
-    out_pre.copy_(v.reshape(out_pre.shape).to(out_pre.dtype))
+    pv = gelu_tanh_grad(v) if out_pre_is_grad else v
+    out_pre.copy_(pv.reshape(out_pre.shape).to(out_pre.dtype))
   if act == ACT_GELU:
     v = gelu_tanh(v)
   if gelu_pre is not None:
-    v = v * gelu_tanh_grad(_as3d(gelu_pre).float())
+    gp = _as3d(gelu_pre).float()
+    v = v * (gp if gelu_pre_is_grad else gelu_tanh_grad(gp))
   if residual is not None:
     v = v + _as3d(residual).float()
   if colsum is not None:
@@ -72,13 +75,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
          colsum: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          accumulate: bool = False, split_k: int = 1, a_ready: Optional[torch.Tensor] = None,
          a_ready_epoch: int = 0, status: Optional[torch.Tensor] = None,
-         num_sms: int = 0) -> torch.Tensor:
+         num_sms: int = 0, out_pre_is_grad: bool = False,
+         gelu_pre_is_grad: bool = False) -> torch.Tensor:
   """``out = epilogue(a @ b^T)``; see ``csrc/vmoe_api.h`` for the epilogue order."""
   if not a.is_cuda:
     return gemm_reference(a, b, a_mn_major=a_mn_major, b_mn_major=b_mn_major, bias=bias,
                           act=act, residual=residual, gelu_pre=gelu_pre, out=out,
                           out_pre=out_pre, colsum=colsum, out_dtype=out_dtype,
-                          accumulate=accumulate)
+                          accumulate=accumulate, out_pre_is_grad=out_pre_is_grad,
+                          gelu_pre_is_grad=gelu_pre_is_grad)
   assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, (a.dtype, b.dtype)
   a3, b3 = _as3d(a), _as3d(b)
   assert a3.stride(-1) == 1 and b3.stride(-1) == 1, "innermost dim must be contiguous"
@@ -144,6 +149,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
   if status is not None:
     args.status = status.data_ptr()
   args.num_sms = num_sms
+  args.c2_gelu_grad = int(out_pre_is_grad)
+  args.pre_is_grad = int(gelu_pre_is_grad)
   rc = _lib.lib().vmoe_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
   _lib.check(rc, "vmoe_gemm_bf16")
   _lib.count_launch()

@@ -20,7 +20,7 @@ import torch.distributed as dist
 
 from vmoe_b200 import moe as moe_core
 from vmoe_b200.ops import _lib, reduce
-from vmoe_b200.ops.functional import bf16_shadow
+from vmoe_b200.ops.functional import _grad_target, bf16_shadow, bias_grad, wgrad
 from vmoe_b200.ops.gemm import ACT_GELU, gemm
 from vmoe_b200.parallel.exchange import ExpertExchange, LOCAL_EXCHANGE
 
@@ -142,13 +142,14 @@ class _FusedMoeFn(torch.autograd.Function):
     need = any(ctx.needs_input_grad)
     pre = torch.empty(xe.shape[0], xe.shape[1], m, dtype=torch.bfloat16,
                       device=x.device) if need else None
-    hid = gemm(xe, w1h, bias=b1, act=ACT_GELU, out_pre=pre)
+    hid = gemm(xe, w1h, bias=b1, act=ACT_GELU, out_pre=pre, out_pre_is_grad=True)
     ye = gemm(hid, w2h, bias=b2)
     ybuf = _a2a_from_experts(ye, exchange)
     out = torch.empty_like(x)
     combine_rows(base_table(ybuf), expert, slot, gate, residual, out, g, s, e, c, k, h)
     ctx.save_for_backward(gate, w1, w2, expert, slot, slot_pair, xe, pre, hid, ybuf)
     ctx.dims = (g, s, e, c, k, h, m)
+    ctx.biases = (b1, b2)
     ctx.exchange = exchange
     ctx.has_res = residual is not None
     return out
@@ -167,13 +168,15 @@ class _FusedMoeFn(torch.autograd.Function):
     combine_bwd(dy, slot_pair, gate, base_table(ybuf), base_table(dybuf), dgate, g, s, e, c, k, h)
     dye = _a2a_to_experts(dybuf, ex)
     el = dye.shape[0]
-    db2 = reduce.colsum(dye)
-    dw2 = torch.zeros(el, h, m, dtype=torch.float32, device=dev)
-    gemm(dye, hid, a_mn_major=True, b_mn_major=True, out=dw2, accumulate=True)
-    db1 = torch.zeros(el, m, dtype=torch.float32, device=dev)
-    dpre = gemm(dye, w2h, b_mn_major=True, gelu_pre=pre, colsum=db1)
-    dw1 = torch.zeros(el, m, h, dtype=torch.float32, device=dev)
-    gemm(dpre, xe, a_mn_major=True, b_mn_major=True, out=dw1, accumulate=True)
+    b1, b2 = ctx.biases
+    db2 = bias_grad(dye, b2)
+    dw2 = wgrad(dye, hid, w2)
+    tgt = _grad_target(b1)
+    db1 = tgt if tgt is not None else torch.zeros(el, m, dtype=torch.float32, device=dev)
+    dpre = gemm(dye, w2h, b_mn_major=True, gelu_pre=pre, gelu_pre_is_grad=True, colsum=db1)
+    if tgt is not None:
+      db1 = None
+    dw1 = wgrad(dpre, xe, w1)
     dxe = gemm(dpre, w1h, b_mn_major=True)
     dxbuf = _a2a_from_experts(dxe, ex)
     # Backward of dispatch: unit-weight combine.

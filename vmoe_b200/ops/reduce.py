@@ -8,9 +8,10 @@ import torch
 from vmoe_b200.ops import _lib
 
 
-def _colsum3(x3: torch.Tensor) -> torch.Tensor:
+def _colsum3(x3: torch.Tensor, out=None) -> torch.Tensor:
   b, r, n = x3.shape
-  out = torch.zeros(b, n, dtype=torch.float32, device=x3.device)
+  if out is None:
+    out = torch.zeros(b, n, dtype=torch.float32, device=x3.device)
   rc = _lib.lib().vmoe_colsum_bf16(ctypes.c_void_p(x3.data_ptr()), ctypes.c_void_p(out.data_ptr()),
                                    ctypes.c_int64(b), ctypes.c_int64(r), ctypes.c_int64(n),
                                    ctypes.c_void_p(_lib.stream_ptr()))
@@ -19,8 +20,28 @@ def _colsum3(x3: torch.Tensor) -> torch.Tensor:
   return out
 
 
-def colsum(x: torch.Tensor) -> torch.Tensor:
-  """fp32 sum over the second-to-last dim: ``(.., R, N) -> (.., N)``."""
+def colsum(x: torch.Tensor, out=None) -> torch.Tensor:
+  """fp32 sum over the second-to-last dim: ``(.., R, N) -> (.., N)``.
+
+  With ``out`` (fp32, contiguous) the sums are *added* to it.
+  """
+  if out is not None:
+    if _direct_ok(x, out):
+      x3 = (x.unsqueeze(0) if x.dim() == 2 else x).contiguous()
+      _colsum3(x3, out=out.reshape(-1, x.shape[-1]))
+    else:
+      out.add_(_colsum(x).reshape(out.shape))
+    return out
+  return _colsum(x)
+
+
+def _direct_ok(x, out) -> bool:
+  return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and
+          (x.dim() == 3 or x.is_contiguous()) and out.is_contiguous() and
+          out.dtype == torch.float32)
+
+
+def _colsum(x: torch.Tensor) -> torch.Tensor:
   if x.is_cuda and x.dtype == torch.bfloat16:
     n = x.shape[-1]
     if (x.dim() == 2 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.stride(0) >= n and
