@@ -159,3 +159,473 @@ def create_train_state(*, model_config: Mapping[str, Any], optimizer_config: Map
   opt = optimizer_lib.create_optimizer(named, total_steps=total_steps, mesh=mesh, **opt_kwargs)
   rngs = misc.make_rngs(tuple(extra_rng_keys) + ("dropout", "gating"), seed)
   return TrainState(model=model, optimizer=opt, step=0, rngs=rngs, mesh=mesh)
+
+
+# ------------------------------------------------------------------------------------ mixup
+def mixup(generator: Optional[torch.Generator], tree, *, concentration: float,
+          shape: Tuple[int, ...] = (1, 2), roll_axis: int = 0):
+  """Mixes every array of ``tree`` with rolled copies of itself using Dirichlet weights.
+
+  ``shape[:-1]`` must broadcast against the leading dims of the arrays and ``shape[-1]`` is
+  the number of examples mixed together. Weights are sorted in decreasing order so that the
+  un-rolled example keeps the largest one; the same weights are used for all arrays.
+  """
+  arrays = list(tree) if isinstance(tree, (tuple, list)) else [tree]
+  if len(shape) < 2:
+    raise ValueError(f"Mixup 'shape' has length {len(shape)}, but it must have length >= 2.")
+  batch_ndim = len(shape) - 1
+  for i, x in enumerate(arrays):
+    try:
+      torch.broadcast_shapes(tuple(x.shape[:batch_ndim]), tuple(shape[:-1]))
+    except RuntimeError:
+      raise ValueError(
+          f"Mixup with inconsistent shapes. The shape of the {i}-th array is "
+          f"{tuple(x.shape)}, but the first {batch_ndim} dims must be broadcastable to "
+          f"{tuple(shape[:-1])}") from None
+    if tuple(x.shape[:batch_ndim]) != tuple(arrays[0].shape[:batch_ndim]):
+      raise ValueError(
+          f"Mixup with inconsistent shapes. The shape of the {i}-th array is "
+          f"{tuple(x.shape)}, but the first {batch_ndim} dims must be equal to "
+          f"{tuple(arrays[0].shape[:batch_ndim])}")
+  if not 0 <= roll_axis < batch_ndim:
+    raise ValueError(
+        f"Mixup 'roll_axis' must be an integer in [0, {batch_ndim}), but got roll_axis = {roll_axis}")
+  if concentration <= 0.0:
+    raise ValueError(
+        f"Mixup 'concentration' must be greater than 0, but got concentration = {concentration}")
+  # Dirichlet(alpha) = normalised Gamma(alpha, 1) samples (drawn on the CPU generator).
+  gamma = torch._standard_gamma(torch.full(tuple(shape), float(concentration)),
+                                generator=generator)
+  alpha = gamma / gamma.sum(-1, keepdim=True).clamp_min(1e-30)
+  alpha = torch.sort(alpha, dim=-1, descending=True).values
+  alpha = torch.movedim(alpha, -1, 0)  # (size, *batch dims)
+  def mix(x):
+    a = alpha.to(device=x.device, dtype=x.dtype if x.is_floating_point() else torch.float32)
+    a = a.reshape(tuple(a.shape) + (1,) * (x.dim() - batch_ndim))
+    return sum(a[i] * torch.roll(x, -i, dims=roll_axis) for i in range(shape[-1]))
+  out = [mix(x) for x in arrays]
+  return type(tree)(out) if isinstance(tree, (tuple, list)) else out[0]
+
+
+def wrap_train_step_with_mixup(train_step_fn, *, concentration: Optional[float] = None,
+                               granularity: str = "device", size: int = 2):
+  """Applies mixup to ``(images, labels)`` before ``train_step_fn``.
+
+  ``granularity``: 'batch' / 'device' share one set of weights per process batch (each
+  process drives one device), 'example' samples weights per example. Mixing partners are
+  taken by rolling inside the local batch, so no cross-device traffic is needed. Uses the
+  state's RNG stream named 'mixup'.
+  """
+  if concentration is None or concentration == 0.0:
+    return train_step_fn
+  if granularity not in ("batch", "device", "example"):
+    raise ValueError(f"Unknown granularity: {granularity!r}")
+
+  def new_train_step_fn(state, images, labels, *args, **kwargs):
+    if not state.rngs or "mixup" not in state.rngs:
+      raise ValueError('Mixup requires an RNG stream with the name "mixup", but only these '
+                       f"were given: {sorted((state.rngs or {}).keys())}")
+    imgs, labs = images.unsqueeze(0), labels.unsqueeze(0)
+    shape = (1, imgs.shape[1], size) if granularity == "example" else (1, 1, size)
+    imgs, labs = mixup(state.rngs["mixup"], (imgs, labs.float()), concentration=concentration,
+                       shape=shape, roll_axis=1)
+    return train_step_fn(state, imgs[0], labs[0], *args, **kwargs)
+
+  return new_train_step_fn
+
+
+# ------------------------------------------------------------------------------------ PGD training
+def wrap_train_step_with_adversarial_attack(train_step_fn, loss_fn, *, max_epsilon: float,
+                                            num_updates: int,
+                                            attack_auxiliary_loss: bool = True):
+  """Adversarial training: images are replaced by PGD adversarial examples (``num_updates``
+  signed-gradient steps of size ``max_epsilon / num_updates``) before the normal step
+  (reference: ``vmoe/train/trainer.py:841-886``)."""
+  from vmoe_b200.projects.adversarial_attacks import attacks
+
+  def new_train_step_fn(state, images, labels, *args, **kwargs):
+    def loss_of(x):
+      logits, metrics = state.model(x)
+      loss = loss_fn(logits, labels).float().sum()
+      if attack_auxiliary_loss:
+        loss = loss + metrics["auxiliary_loss"].float().mean()
+      return loss, None
+    was = state.model.training
+    adv = attacks.stateless_attack_pgd(images, loss_of, max_epsilon=max_epsilon,
+                                       num_updates=num_updates,
+                                       generator=(state.rngs or {}).get("adversarial"))
+    state.model.train(was)
+    return train_step_fn(state, adv.detach(), labels, *args, **kwargs)
+
+  return new_train_step_fn
+
+
+def override_base_config(base, override):
+  """Returns ``base`` updated (recursively) with the keys of ``override``."""
+  from vmoe_b200.utils.config_dict import ConfigDict
+  out = ConfigDict(base.to_dict() if hasattr(base, "to_dict") else dict(base), type_safe=False)
+  if override:
+    out.update(override.to_dict() if hasattr(override, "to_dict") else dict(override))
+  return out
+
+
+# ------------------------------------------------------------------------------------ checkpoints
+class CheckpointManager:
+  """Train-state checkpoints ``<workdir>/ckpt/ckpt_<step>.{index,data-*}`` in the sharded
+  format, saved asynchronously every ``every_steps`` steps; keeps the last ``keep_last``
+  steps plus those that are multiples of ``keep_steps_multiple_of`` (the reference drives
+  Orbax with the same options, ``vmoe/train/trainer.py:134-165``)."""
+
+  def __init__(self, *, workdir: str, every_steps: Optional[int] = None, keep_last: int = 1,
+               keep_steps_multiple_of: Optional[int] = None, wait_seconds: Optional[int] = 300,
+               mesh: Optional[mesh_lib.Mesh] = None, num_shards: Optional[int] = None):
+    import os
+    from vmoe_b200.checkpoints import base as ckpt_base
+    self.dir = os.path.join(workdir, "ckpt")
+    self.prefix = os.path.join(self.dir, "ckpt")
+    self.every_steps = every_steps
+    self.keep_last = keep_last
+    self.keep_multiple = keep_steps_multiple_of
+    self.wait_seconds = wait_seconds
+    self.mesh = mesh or mesh_lib.get_mesh()
+    self.num_shards = num_shards
+    self._pending = None
+    self._pool = ckpt_base.ThreadPool(8)
+    if self.mesh.rank == 0:
+      os.makedirs(self.dir, exist_ok=True)
+    from vmoe_b200.parallel import multihost_utils
+    multihost_utils.sync_devices("checkpoints:create_dir")
+
+  def should_save(self, step: int) -> bool:
+    return bool(self.every_steps) and step % self.every_steps == 0
+
+  def all_steps(self):
+    from vmoe_b200.checkpoints import base as ckpt_base
+    return list(ckpt_base.iterate_complete_steps_for_prefix(self.prefix, suffixes=(".index", ".data")))
+
+  def latest_step(self) -> Optional[int]:
+    steps = self.all_steps()
+    return max(steps) if steps else None
+
+  def wait_until_finished(self):
+    if self._pending is not None:
+      self._pending.get(self.wait_seconds)
+      self._pending = None
+
+  def save(self, step: int, state: TrainState, force: bool = False, last_seen_index=None) -> bool:
+    if not (force or self.should_save(step)):
+      return False
+    from vmoe_b200.checkpoints import partitioned
+    self.wait_until_finished()
+    tree, specs = train_state_to_tree(state)
+    tree["dataset_iterator"] = {"last_seen_index": np.asarray(-1 if last_seen_index is None
+                                                              else last_seen_index)}
+    specs["dataset_iterator"] = {"last_seen_index": None}
+    self._pending = partitioned.save_checkpoint(
+        f"{self.prefix}_{step}", tree, shardings=specs, mesh=self.mesh,
+        num_shards=self.num_shards, thread_pool=self._pool)
+    self._cleanup(step)
+    return True
+
+  def _cleanup(self, current: int):
+    if self.mesh.rank != 0:
+      return
+    import glob, os
+    steps = sorted(set(self.all_steps()) - {current})
+    keep = set(steps[-max(self.keep_last - 1, 0):]) if self.keep_last > 1 else set()
+    for s in steps:
+      if s in keep or (self.keep_multiple and s % self.keep_multiple == 0):
+        continue
+      for f in glob.glob(f"{glob.escape(self.prefix)}_{s}.*"):
+        try:
+          os.remove(f)
+        except OSError:
+          pass
+
+  def close(self):
+    self.wait_until_finished()
+    self._pool.close()
+    self._pool.join()
+
+  def restore(self, state: TrainState, step: Optional[int] = None) -> Optional[int]:
+    from vmoe_b200.checkpoints import partitioned
+    step = self.latest_step() if step is None else step
+    if step is None:
+      return None
+    _, specs = train_state_to_tree(state)
+    specs["dataset_iterator"] = {"last_seen_index": None}
+    tree = partitioned.restore_checkpoint(f"{self.prefix}_{step}", shardings=specs,
+                                          mesh=self.mesh, thread_pool=self._pool)
+    load_train_state_from_tree(state, tree)
+    return step
+
+
+import numpy as np  # noqa: E402  (used by the checkpoint helpers below)
+
+
+def train_state_to_tree(state: TrainState):
+  """``(tree, specs)`` in Flax layout: ``step / params / opt_state / rngs`` with local blocks
+  of expert-sharded leaves and a matching tree of partition specs."""
+  from vmoe_b200.checkpoints import flax_layout
+  params, specs = flax_layout.to_flax(state.model)
+  tree = {"step": np.asarray(state.step), "params": params}
+  spec_tree = {"step": None, "params": specs}
+  if state.optimizer is not None:
+    opt = state.optimizer
+    mu, nu = _moments_to_flax(state, opt)
+    tree["opt_state"] = {"count": np.asarray(opt.step_count), "mu": mu,
+                         "hyperparams": {"learning_rate": np.asarray(opt.last_learning_rate,
+                                                                     dtype=np.float32)}}
+    spec_tree["opt_state"] = {"count": None, "mu": specs, "hyperparams": {"learning_rate": None}}
+    if nu is not None:
+      tree["opt_state"]["nu"] = nu
+      spec_tree["opt_state"]["nu"] = specs
+  if state.rngs:
+    tree["rngs"] = {k: g.get_state().numpy() for k, g in state.rngs.items()}
+    spec_tree["rngs"] = {k: None for k in state.rngs}
+  return tree, spec_tree
+
+
+def _moments_to_flax(state, opt):
+  """Optimizer moments in the same Flax layout as the parameters they belong to."""
+  from vmoe_b200.checkpoints import flax_layout
+  out = []
+  for which in ("mu", "nu"):
+    if which == "nu" and opt.name != "adam":
+      out.append(None)
+      continue
+    saved = {}
+    for b in opt.buckets.values():
+      flat = getattr(b, which)
+      for i, (_, p) in enumerate(b.entries):
+        saved[id(p)] = p.data
+        p.data = b.view_of(flat, i)
+    try:
+      tree, _ = flax_layout.to_flax(state.model)
+    finally:
+      for b in opt.buckets.values():
+        for _, p in b.entries:
+          p.data = saved[id(p)]
+    out.append(tree)
+  return out
+
+
+def load_train_state_from_tree(state: TrainState, tree) -> None:
+  from vmoe_b200.checkpoints import flax_layout
+  state.step = int(np.asarray(tree.get("step", 0)))
+  flax_layout.from_flax(state.model, tree["params"], mesh=state.mesh)
+  opt = state.optimizer
+  if opt is not None and "opt_state" in tree:
+    st = tree["opt_state"]
+    opt.step_count = int(np.asarray(st.get("count", state.step)))
+    for which in ("mu", "nu"):
+      if which not in st or (which == "nu" and opt.name != "adam"):
+        continue
+      saved = {}
+      for b in opt.buckets.values():
+        flat = getattr(b, which)
+        for i, (_, p) in enumerate(b.entries):
+          saved[id(p)] = p.data
+          p.data = b.view_of(flat, i)
+      try:
+        flax_layout.from_flax(state.model, st[which], mesh=state.mesh)
+      finally:
+        for b in opt.buckets.values():
+          for _, p in b.entries:
+            p.data = saved[id(p)]
+  if opt is not None:
+    opt.sync_shadows()
+  if state.rngs and "rngs" in tree:
+    for k, v in tree["rngs"].items():
+      if k in state.rngs:
+        state.rngs[k].set_state(torch.as_tensor(np.asarray(v), dtype=torch.uint8))
+
+
+# ------------------------------------------------------------------------------------ loop
+def _image_size_from_spec(spec) -> Optional[int]:
+  shape = spec.get("image", (None,))[0] if spec else None
+  return int(shape[1]) if shape is not None and len(shape) == 4 else None
+
+
+def create_evaluation_hook(*, base_model_config, writer, progress_hook, datasets, loss_fn,
+                           label_pred_fn, first_step, train_steps, extra_rng_keys=(),
+                           model_overrides=None, state=None, every_steps=None, every_secs=None,
+                           on_steps=None, **kwargs):
+  """Evaluation hook; ``model_overrides`` (e.g. a different capacity factor) build a second,
+  deterministic model that shares the training model's parameters."""
+  from vmoe_b200.evaluate import evaluator
+  on_steps = set(on_steps or []) | {first_step, train_steps}
+  model = state.model
+  if model_overrides:
+    cfg = override_base_config(base_model_config, model_overrides)
+    model = models_lib.create_model(cfg, deterministic=True, mesh=state.mesh,
+                                    image_size=getattr(state.model, "image_size", 224))
+    model.to(next(state.model.parameters()).device)
+    _share_parameters(state.model, model)
+  datasets = {k: v for k, v in datasets.items() if k != "train"}
+  return evaluator.EvaluateMultipleDatasets(
+      model=model, datasets=datasets, loss_fn=loss_fn, label_pred_fn=label_pred_fn,
+      metric_writer=writer, report_progress=progress_hook, every_steps=every_steps,
+      every_secs=every_secs, on_steps=on_steps,
+      input_dtype=None)
+
+
+def _share_parameters(src: torch.nn.Module, dst: torch.nn.Module) -> None:
+  src_params = dict(src.named_parameters())
+  for name, p in dst.named_parameters():
+    if name in src_params and src_params[name].shape == p.shape:
+      p.data = src_params[name].data
+      sp = src_params[name]
+      if hasattr(sp, "_bf16_shadow"):
+        p._bf16_shadow = sp._bf16_shadow
+        p._shadow_version = p._version
+    p.requires_grad_(False)
+
+
+def create_progress_hook(*, writer, first_step, train_steps, **kwargs):
+  from vmoe_b200.train import periodic_actions
+  on_steps = set(kwargs.pop("on_steps", None) or []) | {first_step, train_steps}
+  return periodic_actions.ReportProgress(num_train_steps=train_steps, writer=writer,
+                                         on_steps=on_steps, **kwargs)
+
+
+def create_profile_hook(*, workdir, **kwargs):
+  from vmoe_b200.train import periodic_actions
+  all_processes = kwargs.pop("all_processes", False)
+  hook = periodic_actions.Profile(logdir=workdir, **kwargs)
+  return hook if all_processes else periodic_actions.SingleProcessPeriodicAction(hook)
+
+
+def initialize_train_state_from_checkpoint(*, state: TrainState, name: str, mesh=None,
+                                           **kwargs) -> None:
+  """Runs ``initialize_from_{vmoe,vit,orbax}`` on the Flax-layout view of ``state`` and loads
+  the result back (``kwargs``: prefix/filepath/directory, rules, axis_resources_regexes,
+  raise_if_* switches)."""
+  from vmoe_b200 import initialization
+  fns = {"initialize_from_vmoe": initialization.initialize_from_vmoe,
+         "initialize_from_vit": initialization.initialize_from_vit,
+         "initialize_from_orbax": initialization.initialize_from_orbax}
+  if name not in fns:
+    raise ValueError(f"Unknown initialization function: {name!r}")
+  target, _ = train_state_to_tree(state)
+  target.pop("rngs", None)
+  new_tree = fns[name](target=target, mesh=mesh or state.mesh, **kwargs)
+  load_train_state_from_tree(state, new_tree)
+
+
+def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = None, writer=None):
+  """Trains a model and evaluates it periodically (the ``main`` of ``vmoe_b200.app``)."""
+  import time
+  from vmoe_b200.data import input_pipeline, pjit_utils
+  from vmoe_b200.parallel import multihost_utils
+  from vmoe_b200.train.tree_summarizer import TreeSummarizer
+  from vmoe_b200.utils import metric_writers
+  mesh = mesh or mesh_lib.get_mesh()
+  writer = writer or metric_writers.create_default_writer(workdir, just_logging=mesh.rank > 0)
+  device = (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+            else torch.device("cpu"))
+  datasets = input_pipeline.get_datasets(config.dataset)
+  if "train" not in datasets:
+    raise KeyError(f'You must have a "train" variant of the dataset. Available: {list(datasets)}')
+  train_batch_size = config.dataset.train.batch_size
+  train_steps, train_epochs = get_train_steps_and_epochs(
+      train_steps=config.get("train_steps"), train_epochs=config.get("train_epochs"),
+      train_batch_size=train_batch_size,
+      train_examples=input_pipeline.get_data_num_examples(config.dataset.train))
+  logging.info("Training for %d steps (%g epochs)", train_steps, train_epochs)
+  spec = datasets["train"].peek_spec()
+  image_size = _image_size_from_spec(spec) or 224
+
+  opt_cfg = config.optimizer.to_dict() if hasattr(config.optimizer, "to_dict") else dict(config.optimizer)
+  extra_rng_keys = tuple(config.get("extra_rng_keys", ()) or ())
+  if config.get("mixup") and "mixup" not in extra_rng_keys:
+    extra_rng_keys += ("mixup",)
+  state = create_train_state(model_config=config.model, optimizer_config=opt_cfg,
+                             total_steps=train_steps, mesh=mesh, device=device,
+                             seed=config.get("seed", 0), extra_rng_keys=extra_rng_keys,
+                             image_size=image_size)
+  ckpt_cfg = dict(config.get("save_checkpoint", {}) or {})
+  ckpt_manager = CheckpointManager(workdir=workdir, mesh=mesh, **ckpt_cfg)
+  restored = ckpt_manager.restore(state)
+  if restored is None and config.get("initialization"):
+    init_cfg = config.initialization.to_dict() if hasattr(config.initialization, "to_dict") \
+        else dict(config.initialization)
+    initialize_train_state_from_checkpoint(state=state, mesh=mesh, **init_cfg)
+  init_step = state.step
+  logging.info("Initial step = %d", init_step)
+
+  loss_cfg = dict(config.get("loss", {"name": "softmax_xent"}))
+  train_loss_fn, eval_loss_fn, label_pred_fn = get_loss_fn(**loss_cfg)
+  summarizer = None
+  if config.get("summarize_arrays"):
+    sa = dict(config.summarize_arrays)
+    summarizer = TreeSummarizer(**sa)
+  step_fn = train_step
+  if config.get("adversarial"):
+    step_fn = wrap_train_step_with_adversarial_attack(step_fn, train_loss_fn,
+                                                      **dict(config.adversarial))
+  if config.get("mixup"):
+    mix = dict(config.mixup)
+    mix.pop("partition_spec", None)
+    step_fn = wrap_train_step_with_mixup(step_fn, **mix)
+  microsteps = config.get("microsteps")
+
+  progress_hook = create_progress_hook(writer=writer, first_step=init_step + 1,
+                                       train_steps=train_steps,
+                                       **dict(config.get("report_progress", {}) or {}))
+  eval_cfg = dict(config.get("evaluate", {}) or {})
+  eval_cfg.pop("seed", None)
+  evaluation_hook = create_evaluation_hook(
+      base_model_config=config.model, writer=writer, progress_hook=progress_hook,
+      datasets=datasets, loss_fn=eval_loss_fn, label_pred_fn=label_pred_fn,
+      first_step=init_step + 1, train_steps=train_steps, extra_rng_keys=extra_rng_keys,
+      state=state, **eval_cfg)
+  profile_hook = None
+  if config.get("profile"):
+    profile_hook = create_profile_hook(workdir=workdir, **dict(config.profile))
+  fewshot_hook = None
+  if config.get("fewshot"):
+    from vmoe_b200.evaluate import fewshot as fewshot_lib
+    fs = dict(config.fewshot)
+    fs_model_cfg = override_base_config(config.model, {"num_classes": None})
+    fs_model = models_lib.create_model(fs_model_cfg, deterministic=True, mesh=mesh,
+                                       image_size=image_size).to(device)
+    _share_parameters(state.model, fs_model)
+    fewshot_hook = fewshot_lib.FewShotPeriodicAction(
+        model=fs_model, metric_writer=writer, report_progress=progress_hook, **fs)
+
+  dtype = getattr(state.model, "dtype", None)
+  def batches():
+    it = iter(datasets["train"])
+    while True:
+      yield next(it)
+  tr_iter = pjit_utils.prefetch_to_device(
+      batches(), size=int(config.dataset.train.get("prefetch_device", 2) or 2), device=device)
+
+  multihost_utils.sync_devices("training:start")
+  if init_step == 0 and ckpt_cfg.get("every_steps"):
+    ckpt_manager.save(0, state, force=True)
+  t_start = time.time()
+  metrics = {}
+  for step in range(init_step + 1, train_steps + 1):
+    batch = next(tr_iter)
+    if profile_hook is not None:
+      profile_hook(step)
+    _, metrics = step_fn(state, batch["image"], batch["labels"], train_loss_fn,
+                         microsteps=microsteps, summarizer=summarizer)
+    progress_hook(step, scalar_metrics={"train": {k: v for k, v in metrics.items()
+                                                  if not isinstance(v, Mapping)}})
+    with progress_hook.timed("ckpt", wait_jax_async_dispatch=False):
+      ckpt_manager.save(step, state)
+    evaluation_hook(step)
+    if fewshot_hook is not None:
+      fewshot_hook(step)
+  ckpt_manager.wait_until_finished()
+  if ckpt_cfg.get("every_steps") and train_steps > init_step and ckpt_manager.latest_step() != train_steps:
+    ckpt_manager.save(train_steps, state, force=True)
+    ckpt_manager.wait_until_finished()
+  ckpt_manager.close()
+  multihost_utils.sync_devices("training:completed")
+  logging.info("Training completed in %.1f s.", time.time() - t_start)
+  writer.flush()
+  return state, metrics
