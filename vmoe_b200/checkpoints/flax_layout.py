@@ -60,6 +60,9 @@ def _entries(model: torch.nn.Module):
       if mod.bias is not None:
         yield join("bias"), mod.bias, "same", None
         claimed.add(id(mod.bias))
+    elif type(mod).__name__ == "_MemberGating":
+      yield join("kernel"), mod.weight, "member_gating_w", None
+      claimed.add(id(mod.weight))
     elif isinstance(mod, torch.nn.Linear):
       yield join("kernel"), mod.weight, "dense_w", None
       claimed.add(id(mod.weight))
@@ -94,6 +97,8 @@ def _to_flax_array(p: torch.Tensor, kind: str, extra) -> np.ndarray:
   elif kind == "attn_out_w":
     h, d = extra
     out = t.t().reshape(h, d, t.shape[0])
+  elif kind == "member_gating_w":
+    out = t.permute(2, 0, 1)  # (M, E/M, H) -> (H, M, E/M)
   elif kind == "mlp_w":
     out = t.transpose(1, 2)
   elif kind == "mlp_b":
@@ -121,6 +126,8 @@ def _from_flax_array(value: np.ndarray, p: torch.Tensor, kind: str, extra) -> to
     return v.reshape(-1)
   if kind == "attn_out_w":
     return v.reshape(-1, v.shape[-1]).t()
+  if kind == "member_gating_w":
+    return v.permute(1, 2, 0)
   if kind == "mlp_w":
     return v.transpose(1, 2)
   if kind == "mlp_w_dense":

@@ -106,7 +106,10 @@ class NoisyTopExpertsPerItemRouter(_RouterBase):
       raise ValueError(
           "num_experts >= num_selected_experts >= 1, but got "
           f"num_experts = {num_experts} and num_selected_experts = {self.num_selected_experts}.")
-    logits = self.gating_logits(inputs)
+    return self._gates_and_metrics_from_logits(self.gating_logits(inputs), num_experts)
+
+  def _gates_and_metrics_from_logits(self, logits: Tensor, num_experts: int, noise=None):
+    """``logits (G, S, E)`` -> (softmax gates used for dispatch, per-group metrics)."""
     gates = torch.softmax(logits, dim=-1)
     importance_loss = self._importance_auxiliary_loss(gates)
     if self.is_deterministic() or self.noise_std == 0.0:
@@ -119,7 +122,10 @@ class NoisyTopExpertsPerItemRouter(_RouterBase):
       }
       return gates, metrics
     noise_std = self.noise_std / num_experts
-    logits_noisy = logits + self.sample_noise(logits)
+    if noise is None:
+      noise = (self.injected_noise.to(logits) if self.injected_noise is not None
+               else torch.randn_like(logits))
+    logits_noisy = logits + noise * noise_std
     gates_noisy = torch.softmax(logits_noisy, dim=-1)
     load_loss = self._load_auxiliary_loss(logits, logits_noisy, noise_std,
                                           self.num_selected_experts)

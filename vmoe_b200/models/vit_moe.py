@@ -184,6 +184,7 @@ class MlpMoeBlock(nn.Module):
   def create_router(self, hidden_size, num_experts, router, dtype) -> nn.Module:
     kwargs = dict(num_experts=num_experts, **(router or {}))
     name = kwargs.pop("name", "NoisyTopExpertsPerItemRouter")
+    _load_project_routers()
     cls, args, kwargs2 = parse_call(name, default_module=ROUTERS)
     merged = {**kwargs2, **kwargs}
     return cls(*args, hidden_size=hidden_size, dtype=dtype, exchange=self.exchange, **merged)
@@ -513,6 +514,18 @@ ROUTERS: Dict[str, Any] = {
     "NoisyTopExpertsPerItemRouter": routing.NoisyTopExpertsPerItemRouter,
     "NoisyTopItemsPerExpertRouter": routing.NoisyTopItemsPerExpertRouter,
 }
+
+
+def _load_project_routers() -> None:
+  """Imports the router modules that live under ``vmoe_b200.projects`` (they register
+  themselves), so that configs can name e.g. ``'SoftRouter'`` without a module path."""
+  import importlib
+  for mod in ("vmoe_b200.projects.soft_moe.router",
+              "vmoe_b200.projects.sparsity_constrained_ot.ot_routing"):
+    try:
+      importlib.import_module(mod)
+    except ImportError:
+      pass
 
 
 def register_router(name: str, cls) -> None:
