@@ -1,0 +1,96 @@
+"""Worker for the multi-process CPU (gloo) tests; launched by tests/test_distributed_cpu.py."""
+import json
+import logging
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from vmoe_b200.configs.vmoe_paper import common  # noqa: E402
+from vmoe_b200.parallel import mesh as mesh_lib  # noqa: E402
+from vmoe_b200.parallel import multihost_utils  # noqa: E402
+from vmoe_b200.train import trainer  # noqa: E402
+
+
+def small_config():
+  cfg = common.get_vmoe_config("ViT-S/32, E=8, K=2, Last 2", 64, 10)
+  cfg.hidden_size = 64
+  cfg.representation_size = None
+  cfg.head_kernel_zero_init = False
+  cfg.encoder.num_layers = 4
+  cfg.encoder.mlp_dim = 128
+  cfg.encoder.num_heads = 4
+  cfg.encoder.moe.layers = (1, 3)
+  cfg.encoder.moe.num_experts = 4
+  cfg.encoder.moe.group_size = 10  # two images of 5 tokens
+  cfg.encoder.moe.split_rngs = True
+  cfg.encoder.moe.router.noise_std = 0.0
+  cfg.encoder.moe.router.dispatcher.batch_priority = True
+  return cfg
+
+
+def main():
+  logging.disable(logging.WARNING)
+  mode, outdir = sys.argv[1], sys.argv[2]
+  mesh_lib.init_distributed(backend="gloo")
+  world = dist.get_world_size() if dist.is_initialized() else 1
+  rank = dist.get_rank() if dist.is_initialized() else 0
+  partitions = int(os.environ.get("EXPERT_PARTITIONS", "2"))
+  mesh = mesh_lib.get_auto_logical_mesh(partitions)
+  mesh_lib.set_mesh(mesh)
+  if mode == "barrier_mismatch":
+    try:
+      multihost_utils.sync_devices("same" if rank == 0 else "different", main_process=rank)
+      ok = "no error"
+    except ValueError as e:
+      ok = "ValueError"
+    json.dump({"result": ok}, open(os.path.join(outdir, f"r{rank}.json"), "w"))
+    return
+  multihost_utils.sync_devices("start")
+  state = trainer.create_train_state(
+      model_config=small_config(),
+      optimizer_config=dict(name="adam", learning_rate=1e-3, weight_decay=0.1),
+      total_steps=10, mesh=mesh, seed=0, image_size=64)
+  gen = torch.Generator().manual_seed(123)
+  images = torch.rand(8, 64, 64, 3, generator=gen) * 2 - 1
+  labels = torch.nn.functional.one_hot(torch.randint(0, 10, (8,), generator=gen), 10).float()
+  per = 8 // world
+  loss_fn, _, _ = trainer.get_loss_fn("softmax_xent")
+  _, metrics = trainer.train_step(state, images[rank * per:(rank + 1) * per],
+                                  labels[rank * per:(rank + 1) * per], loss_fn)
+  out = {"main_loss": float(metrics["main_loss"]), "grad_norm": float(metrics["global_norm/grads"])}
+  # Save and reload the sharded checkpoint, then compare against the live state.
+  mgr = trainer.CheckpointManager(workdir=outdir, every_steps=1, mesh=mesh)
+  mgr.save(1, state, force=True)
+  mgr.wait_until_finished()
+  multihost_utils.sync_devices("saved")
+  state2 = trainer.create_train_state(
+      model_config=small_config(),
+      optimizer_config=dict(name="adam", learning_rate=1e-3, weight_decay=0.1),
+      total_steps=10, mesh=mesh, seed=1, image_size=64)
+  restored = mgr.restore(state2)
+  same = all(torch.equal(a.data, b.data) for a, b in
+             zip(state.model.parameters(), state2.model.parameters()))
+  out.update(restored=restored, same=bool(same), step=state2.step)
+  mgr.close()
+  # Full (global) parameter values for comparison across world sizes.
+  from vmoe_b200.checkpoints import partitioned
+  full = partitioned.restore_checkpoint(os.path.join(outdir, "ckpt", "ckpt_1"),
+                                        mesh=mesh_lib.Mesh())
+  w = full["params"]["Encoder"]["encoderblock_1"]["Moe"]["Mlp"]["Dense_0"]["kernel"]
+  h = full["params"]["head"]["kernel"]
+  out.update(expert_kernel_sum=float(np.abs(w).sum()), expert_kernel_shape=list(w.shape),
+             head_sum=float(np.abs(h).sum()),
+             q_sum=float(np.abs(full["params"]["Encoder"]["encoderblock_0"]["SelfAttention"]["query"]["kernel"]).sum()))
+  json.dump(out, open(os.path.join(outdir, f"r{rank}.json"), "w"))
+  if dist.is_initialized():
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+  main()

@@ -20,14 +20,16 @@ class _AllToAll(torch.autograd.Function):
   @staticmethod
   def forward(ctx, x, group):
     ctx.group = group
+    x = x.contiguous()
     out = torch.empty_like(x)
-    dist.all_to_all_single(out, x.contiguous(), group=group)
+    dist.all_to_all_single(out, x, group=group)
     return out
 
   @staticmethod
   def backward(ctx, grad):
+    grad = grad.contiguous()  # the incoming gradient is usually a transposed view
     out = torch.empty_like(grad)
-    dist.all_to_all_single(out, grad.contiguous(), group=ctx.group)
+    dist.all_to_all_single(out, grad, group=ctx.group)
     return out, None
 
 
