@@ -58,13 +58,15 @@ struct GemmParams {
   int tma_store;  // bf16 outputs go through smem staging + TMA stores
   int c2_gelu_grad;  // C2 receives gelu'(pre-activation) instead of the pre-activation
   int pre_is_grad;   // gelu_pre already holds gelu'(x): plain multiply
+  int mt_offset;     // rotation of the m-tile order
 };
 
 struct TileCoord {
   int b, mt, nt, ks;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(int tile, int num_m, int num_n, int split_k) {
+__device__ __forceinline__ TileCoord decode_tile(int tile, int num_m, int num_n, int split_k,
+                                                 int mt_offset = 0) {
   // n fastest, then split, then m, then batch: CTAs that run together share an A panel
   // through L2 while the (small) B matrix stays L2 resident.
   TileCoord t;
@@ -72,7 +74,7 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int num_m, int num_n,
   tile /= num_n;
   t.ks = tile % split_k;
   tile /= split_k;
-  t.mt = tile % num_m;
+  t.mt = (tile % num_m + mt_offset) % num_m;
   t.b = tile / num_m;
   return t;
 }
@@ -161,7 +163,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k);
+        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, p.mt_offset);
         const int m0 = t.mt * BM, n0 = t.nt * BN;
         const int kt0 = t.ks * k_per_split;
         const int kt1 = min(k_tiles, kt0 + k_per_split);
@@ -235,7 +237,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k);
+        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, p.mt_offset);
         const int kt0 = t.ks * k_per_split;
         const int kt1 = min(k_tiles, kt0 + k_per_split);
         const int slot = local & 1;
@@ -283,7 +285,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-      const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k);
+      const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, p.mt_offset);
       const int kt0 = t.ks * k_per_split;
       const int kt1 = min(k_tiles, kt0 + k_per_split);
       const int slot = local & 1;
@@ -702,6 +704,7 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   p.a_ready_epoch = a->a_ready_epoch;
   p.c2_gelu_grad = a->c2_gelu_grad;
   p.pre_is_grad = a->pre_is_grad;
+  p.mt_offset = a->mt_offset > 0 ? static_cast<int>(a->mt_offset % ((a->M + BM - 1) / BM)) : 0;
 
   static int sm_count = 0;
   static bool attr_set = false;

@@ -52,6 +52,7 @@ typedef struct VmoeGemmArgs {
   int32_t num_sms;   // CTAs to launch at most (0: all SMs of the device)
   int32_t c2_gelu_grad;  // with act == 1: C2 receives gelu'(v) instead of v
   int32_t pre_is_grad;   // gelu_pre already holds gelu'(x): multiply by it as is
+  int32_t mt_offset;     // m-tiles are visited starting from this tile (rotation)
 } VmoeGemmArgs;
 
 VMOE_API int vmoe_gemm_bf16(const VmoeGemmArgs* args, vmoe_stream_t stream);
@@ -144,6 +145,26 @@ typedef struct VmoeAttnArgs {
 } VmoeAttnArgs;
 VMOE_API int vmoe_attention_fwd(const VmoeAttnArgs* args, vmoe_stream_t stream);
 VMOE_API int vmoe_attention_bwd(const VmoeAttnArgs* args, vmoe_stream_t stream);
+
+// ----------------------------------------------------------------------------- expert-parallel P2P
+// Gathers the rows routed to every expert and stores them into the owning GPU's row buffer
+// (dst_base[e] = address of this rank's block of expert e, possibly peer memory). For every
+// 128-row chunk written, the number of rows is added (release, system scope) to the tile
+// counters at flag_base[e] (the expert's counters on its owner; tile = buffer row / 128,
+// where this rank's block starts at row rank * groups * c). flag_base may be NULL. With
+// `weight`, rows are scaled by it and, if ybuf_base/dgate are given, dgate[pair] = <x, ybuf>.
+VMOE_API int vmoe_moe_push_rows(const void* x, const int32_t* slot_pair, const float* weight,
+                                const uint64_t* dst_base, const uint64_t* flag_base,
+                                const uint64_t* ybuf_base, float* dgate, int64_t groups, int64_t s,
+                                int64_t e, int64_t c, int64_t k, int64_t h,
+                                int64_t experts_per_rank, int64_t ep, int64_t rank,
+                                vmoe_stream_t stream);
+// *flag += value with a system-scope release, ordered after all earlier work of the stream.
+VMOE_API int vmoe_signal(uint32_t* flag, uint32_t value, vmoe_stream_t stream);
+// Blocks the stream until counters[i] >= target for all i < n; gives up after limit_cycles
+// (0: the library default) and sets the peer-timeout bit in *status.
+VMOE_API int vmoe_wait_counters(const uint32_t* counters, int32_t n, uint32_t target,
+                                uint32_t* status, int64_t limit_cycles, vmoe_stream_t stream);
 
 // Last error text of the calling thread ("" if none).
 VMOE_API const char* vmoe_last_error(void);

@@ -122,6 +122,193 @@ def _a2a_from_experts(buf: torch.Tensor, ex: ExpertExchange) -> torch.Tensor:
   return recv
 
 
+def push_rows(x, slot_pair, weight, dst_table, flag_table, ybuf_table, dgate, g, s, e, c, k, h,
+              el, ep, rank):
+  rc = _lib.lib().vmoe_moe_push_rows(
+      _vp(x.data_ptr()), _vp(slot_pair.data_ptr()), _vp(_lib.ptr(weight)),
+      _vp(dst_table.data_ptr()), _vp(_lib.ptr(flag_table)), _vp(_lib.ptr(ybuf_table)),
+      _vp(_lib.ptr(dgate)), _i64(g), _i64(s), _i64(e), _i64(c), _i64(k), _i64(h), _i64(el),
+      _i64(ep), _i64(rank), _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_moe_push_rows")
+  _lib.count_launch()
+
+
+def signal(addr: int, value: int = 1):
+  rc = _lib.lib().vmoe_signal(_vp(addr), ctypes.c_uint32(value), _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_signal")
+  _lib.count_launch()
+
+
+def wait_counters(counters: torch.Tensor, n: int, target: int, status=None, limit_cycles: int = 0):
+  rc = _lib.lib().vmoe_wait_counters(_vp(counters.data_ptr()), ctypes.c_int32(n),
+                                     ctypes.c_uint32(target & 0xFFFFFFFF), _vp(_lib.ptr(status)),
+                                     _i64(limit_cycles), _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_wait_counters")
+  _lib.count_launch()
+
+
+class LayerComm:
+  """Symmetric buffers and address tables of one MoE layer for the peer-to-peer path.
+
+  Per rank: XE / DYE ``(E_local, ep*R, H)`` receive the rows dispatched to the local experts
+  (forward / backward), YB / DXB ``(E, R, H)`` receive the expert outputs coming home, plus
+  per-tile arrival counters for XE / DYE and per-source completion counters for YB / DXB.
+  ``R = G*C`` rows per (expert, source rank).
+  """
+
+  def __init__(self, exchange: ExpertExchange, e: int, r: int, h: int, device):
+    from vmoe_b200.parallel import symm
+    ep = exchange.size
+    self.ep, self.e, self.el, self.r, self.h = ep, e, e // ep, r, h
+    self.tiles = (ep * r + 127) // 128
+    blk = e * r * h * 2
+    fl_tiles = (self.el * self.tiles * 4 + 255) // 256 * 256
+    fl_src = 256
+    self.off = {"XE": 0, "YB": blk, "DYE": 2 * blk, "DXB": 3 * blk,
+                "FX": 4 * blk, "FDY": 4 * blk + fl_tiles, "FY": 4 * blk + 2 * fl_tiles,
+                "FDX": 4 * blk + 2 * fl_tiles + fl_src}
+    self.buf = symm.SymmetricBuffer(4 * blk + 2 * fl_tiles + 2 * fl_src, exchange.group, device)
+    self.rank = self.buf.rank
+    b = self.buf
+    self.xe = b.local(self.off["XE"], (self.el, ep * r, h), torch.bfloat16)
+    self.dye = b.local(self.off["DYE"], (self.el, ep * r, h), torch.bfloat16)
+    self.yb = b.local(self.off["YB"], (e, r, h), torch.bfloat16)
+    self.dxb = b.local(self.off["DXB"], (e, r, h), torch.bfloat16)
+    self.fx = b.local(self.off["FX"], (self.el * self.tiles,), torch.int32)
+    self.fdy = b.local(self.off["FDY"], (self.el * self.tiles,), torch.int32)
+    self.fy = b.local(self.off["FY"], (64,), torch.int32)
+    self.fdx = b.local(self.off["FDX"], (64,), torch.int32)
+    self.status = torch.zeros(1, dtype=torch.int32, device=device)
+    self.epoch = {"x": 0, "y": 0, "dy": 0, "dx": 0}
+
+    def table(data_key, flag_key):
+      dst, flg = [], []
+      for ee in range(e):
+        owner, loc = ee // self.el, ee % self.el
+        dst.append(b.ptrs[owner] + self.off[data_key] + (loc * ep + self.rank) * r * h * 2)
+        flg.append(b.ptrs[owner] + self.off[flag_key] + loc * self.tiles * 4)
+      mk = lambda v: torch.tensor(v, dtype=torch.int64, device=device)
+      return mk(dst), mk(flg)
+
+    self.push_x, self.flag_x = table("XE", "FX")
+    self.push_dy, self.flag_dy = table("DYE", "FDY")
+    self.yb_table = _base_table(self.yb)
+    self.dxb_table = _base_table(self.dxb)
+    self.mt_offset = (self.rank * r) // 128
+
+  def home_out(self, key: str, src: int) -> torch.Tensor:
+    """View of source rank ``src``'s YB/DXB slice that receives this rank's experts."""
+    off = self.off[key] + self.rank * self.el * self.r * self.h * 2
+    return self.buf.peer(src, off, (self.el, self.r, self.h), torch.bfloat16)
+
+  def done_flag_addr(self, key: str, src: int) -> int:
+    return self.buf.ptrs[src] + self.off[key] + self.rank * 4
+
+
+_LAYER_COMMS: dict = {}
+
+
+def layer_comm(owner, exchange: ExpertExchange, e: int, r: int, h: int, device) -> LayerComm:
+  """The ``LayerComm`` of a MoE layer (``owner`` identifies the layer), created on first use.
+  Creation is a collective: all ranks of the expert group must reach it in the same order."""
+  key = (id(owner), e, r, h)
+  comm = _LAYER_COMMS.get(key)
+  if comm is None:
+    comm = LayerComm(exchange, e, r, h, device)
+    _LAYER_COMMS[key] = comm
+  return comm
+
+
+def p2p_enabled(exchange: ExpertExchange) -> bool:
+  import os
+  from vmoe_b200.parallel import symm
+  return (exchange.size > 1 and os.environ.get("VMOE_B200_P2P", "1") != "0" and symm.available()
+          and dist.is_initialized() and dist.get_backend(exchange.group) == "nccl")
+
+
+class _P2PMoeFn(torch.autograd.Function):
+  """Expert-parallel MoE layer over NVLink peer memory (no NCCL all-to-all).
+
+  Forward: push rows into the owners' XE buffers (arrival counters) -> GEMM1 consumes tiles as
+  they arrive -> GEMM2 per source rank stores its output tiles into that rank's YB buffer and
+  bumps its completion counter -> combine at home once all sources are complete.
+  """
+
+  @staticmethod
+  def forward(ctx, x, gate, w1, b1, w2, b2, residual, expert, slot, slot_pair, capacity,
+              exchange, comm):
+    g, s, h = x.shape
+    k = expert.shape[-1]
+    e = slot_pair.shape[1]
+    c = capacity
+    r = g * c
+    ep, el, rank = comm.ep, comm.el, comm.rank
+    x = x.contiguous()
+    gate = gate.contiguous().float()
+    w1h, w2h = bf16_shadow(w1), bf16_shadow(w2)
+    m = w1.shape[1]
+    # All ranks are past their previous use of this layer's buffers.
+    comm.buf.barrier()
+    for key in ("x", "y"):
+      comm.epoch[key] += 1
+    push_rows(x, slot_pair, None, comm.push_x, comm.flag_x, None, None, g, s, e, c, k, h, el, ep,
+              rank)
+    need = any(ctx.needs_input_grad)
+    pre = torch.empty(el, ep * r, m, dtype=torch.bfloat16, device=x.device) if need else None
+    hid = gemm(comm.xe, w1h, bias=b1, act=ACT_GELU, out_pre=pre, out_pre_is_grad=True,
+               a_ready=comm.fx, a_ready_epoch=comm.epoch["x"], status=comm.status,
+               mt_offset=comm.mt_offset)
+    for i in range(ep):
+      src = (rank + i) % ep
+      gemm(hid[:, src * r:(src + 1) * r], w2h, bias=b2, out=comm.home_out("YB", src))
+      signal(comm.done_flag_addr("FY", src))
+    wait_counters(comm.fy, ep, comm.epoch["y"], comm.status)
+    out = torch.empty_like(x)
+    combine_rows(comm.yb_table, expert, slot, gate, residual, out, g, s, e, c, k, h)
+    ctx.save_for_backward(gate, w1, w2, expert, slot, slot_pair, pre, hid)
+    ctx.dims = (g, s, e, c, k, h, m)
+    ctx.comm = comm
+    ctx.biases = (b1, b2)
+    ctx.has_res = residual is not None
+    return out
+
+  @staticmethod
+  def backward(ctx, dy):
+    gate, w1, w2, expert, slot, slot_pair, pre, hid = ctx.saved_tensors
+    g, s, e, c, k, h, m = ctx.dims
+    comm = ctx.comm
+    ep, el, rank, r = comm.ep, comm.el, comm.rank, g * c
+    w1h, w2h = bf16_shadow(w1), bf16_shadow(w2)
+    dy = dy.contiguous()
+    dev = dy.device
+    for key in ("dy", "dx"):
+      comm.epoch[key] += 1
+    dgate = torch.zeros(g, s, k, dtype=torch.float32, device=dev)
+    push_rows(dy, slot_pair, gate, comm.push_dy, comm.flag_dy, comm.yb_table, dgate, g, s, e, c, k,
+              h, el, ep, rank)
+    b1, b2 = ctx.biases
+    tgt = _grad_target(b1)
+    db1 = tgt if tgt is not None else torch.zeros(el, m, dtype=torch.float32, device=dev)
+    dpre = gemm(comm.dye, w2h, b_mn_major=True, gelu_pre=pre, gelu_pre_is_grad=True, colsum=db1,
+                a_ready=comm.fdy, a_ready_epoch=comm.epoch["dy"], status=comm.status,
+                mt_offset=comm.mt_offset)
+    if tgt is not None:
+      db1 = None
+    # Every tile of dye has arrived once the GEMM above has run.
+    db2 = bias_grad(comm.dye, b2)
+    dw2 = wgrad(comm.dye, hid, w2)
+    dw1 = wgrad(dpre, comm.xe, w1)
+    for i in range(ep):
+      src = (rank + i) % ep
+      gemm(dpre[:, src * r:(src + 1) * r], w1h, b_mn_major=True, out=comm.home_out("DXB", src))
+      signal(comm.done_flag_addr("FDX", src))
+    wait_counters(comm.fdx, ep, comm.epoch["dx"], comm.status)
+    dx = torch.empty(g, s, h, dtype=torch.bfloat16, device=dev)
+    combine_rows(comm.dxb_table, expert, slot, None, None, dx, g, s, e, c, k, h)
+    d_res = dy if ctx.has_res else None
+    return dx, dgate, dw1, db1, dw2, db2, d_res, None, None, None, None, None, None
+
+
 class _FusedMoeFn(torch.autograd.Function):
 
   @staticmethod
@@ -224,6 +411,12 @@ class FusedTopKDispatcher(moe_core.BaseDispatcher):
     if mlp.training and getattr(mlp, "dropout_rate", 0.0) > 0:
       out = moe_core.sparse_moe_apply(mlp, self._generic(), x)
       return out if residual is None else out + residual
+    if p2p_enabled(self.exchange):
+      g, s, h = x.shape
+      comm = layer_comm(mlp, self.exchange, self.num_experts, g * self.capacity, h, x.device)
+      return _P2PMoeFn.apply(x, self.combine_weights, mlp.w1, mlp.b1, mlp.w2, mlp.b2, residual,
+                             self.expert, self.slot, self.slot_pair, self.capacity,
+                             self.exchange, comm)
     return _FusedMoeFn.apply(x, self.combine_weights, mlp.w1, mlp.b1, mlp.w2, mlp.b2, residual,
                              self.expert, self.slot, self.slot_pair, self.capacity,
                              self.exchange)
