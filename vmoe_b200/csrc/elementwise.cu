@@ -46,7 +46,37 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ----------------------------------------------------------------------------- LayerNorm
-// One warp per row; lane l owns the 8-element chunks l, l+32, ... (MAXC of them at most).
+// One warp per row; lane l owns the 8-element chunks l, l+32, ... (MAXC of them at most), so
+// its gamma/beta values never change and live in registers. The next row's data is fetched
+// (as packed bf16) while the current row is reduced, which keeps two rows per warp in flight.
+template <int MAXC>
+__device__ __forceinline__ void ln_load_row(const __nv_bfloat16* base, long long row, int h,
+                                            int lane, int chunks, uint4 (&q)[MAXC]) {
+  const uint4* r = reinterpret_cast<const uint4*>(base + row * h);
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + 32 * c;
+    q[c] = ch < chunks ? __ldg(r + ch) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <int MAXC>
+__device__ __forceinline__ void ln_load_affine(const float* p, int lane, int chunks, float fill,
+                                               float (&v)[MAXC][8]) {
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + 32 * c;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[c][i] = fill;
+    if (p != nullptr && ch < chunks) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(p + ch * 8));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(p + ch * 8) + 1);
+      v[c][0] = a.x; v[c][1] = a.y; v[c][2] = a.z; v[c][3] = a.w;
+      v[c][4] = b.x; v[c][5] = b.y; v[c][6] = b.z; v[c][7] = b.w;
+    }
+  }
+}
+
 template <int MAXC>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
@@ -57,18 +87,20 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const int chunks = h >> 3;
+  float gm[MAXC][8], bt[MAXC][8];
+  ln_load_affine<MAXC>(gamma, lane, chunks, 1.0f, gm);
+  ln_load_affine<MAXC>(beta, lane, chunks, 0.0f, bt);
+  uint4 cur[MAXC], nxt[MAXC];
+  if (warp < rows) ln_load_row<MAXC>(x, warp, h, lane, chunks, cur);
   for (long long row = warp; row < rows; row += nwarps) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * h);
+    if (row + nwarps < rows) ln_load_row<MAXC>(x, row + nwarps, h, lane, chunks, nxt);
     float v[MAXC][8];
     float s = 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
-      const int ch = lane + 32 * c;
-      if (ch < chunks) {
-        unpack8(__ldg(xr + ch), v[c]);
+      unpack8(cur[c], v[c]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s += v[c][i];
-      }
+      for (int i = 0; i < 8; ++i) s += v[c][i];  // chunks past the row end hold zeros
     }
     const float mean = warp_sum(s) / h;
     float sq = 0.f;
@@ -90,12 +122,7 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
       if (ch < chunks) {
         float o[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float t = (v[c][i] - mean) * rstd;
-          if (gamma) t *= __ldg(gamma + ch * 8 + i);
-          if (beta) t += __ldg(beta + ch * 8 + i);
-          o[i] = t;
-        }
+        for (int i = 0; i < 8; ++i) o[i] = (v[c][i] - mean) * rstd * gm[c][i] + bt[c][i];
         yr[ch] = pack8(o);
       }
     }
@@ -103,20 +130,24 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
       if (mean_out) mean_out[row] = mean;
       if (rstd_out) rstd_out[row] = rstd;
     }
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) cur[c] = nxt[c];
   }
 }
 
-// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) with g = dy * gamma;
-// dgamma += sum_rows dy * xhat, dbeta += sum_rows dy (per-warp register partials, one atomic
-// per column and CTA at the end). `dres`, if given, is added to dx (gradient of a residual
-// branch that bypasses the norm).
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) with g = dy * gamma (+ dres if given).
+// Every warp keeps partial sums of dgamma = sum_rows dy * xhat and dbeta = sum_rows dy for its
+// own columns in registers; at the end the CTA adds them up in shared memory and writes one
+// row of partials to `partial` ([gridDim.x][2*h], scratch memory). A second kernel
+// (ln_reduce_partials_kernel) sums the rows of `partial` into dgamma / dbeta, so the result
+// does not depend on the order in which CTAs finish.
 template <int MAXC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                     __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
-                     float* __restrict__ dbeta, long long rows, int h) {
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, long long rows,
+                     int h) {
   extern __shared__ float red[];  // [2][h]
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -124,32 +155,39 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   const int chunks = h >> 3;
   for (int i = threadIdx.x; i < 2 * h; i += blockDim.x) red[i] = 0.f;
   __syncthreads();
+  float gm[MAXC][8];
+  ln_load_affine<MAXC>(gamma, lane, chunks, 1.0f, gm);
   float ag[MAXC][8], ab[MAXC][8];
 #pragma unroll
   for (int c = 0; c < MAXC; ++c)
 #pragma unroll
     for (int i = 0; i < 8; ++i) ag[c][i] = ab[c][i] = 0.f;
+  uint4 xc[MAXC], dc[MAXC], xn[MAXC], dn[MAXC];
+  if (warp < rows) {
+    ln_load_row<MAXC>(x, warp, h, lane, chunks, xc);
+    ln_load_row<MAXC>(dy, warp, h, lane, chunks, dc);
+  }
   for (long long row = warp; row < rows; row += nwarps) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * h);
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * h);
+    if (row + nwarps < rows) {
+      ln_load_row<MAXC>(x, row + nwarps, h, lane, chunks, xn);
+      ln_load_row<MAXC>(dy, row + nwarps, h, lane, chunks, dn);
+    }
     const float mean = __ldg(mean_in + row), rstd = __ldg(rstd_in + row);
-    float xh[MAXC][8], g[MAXC][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
-      const int ch = lane + 32 * c;
-      if (ch < chunks) {
+      if (lane + 32 * c < chunks) {
         float xv[8], dv[8];
-        unpack8(__ldg(xr + ch), xv);
-        unpack8(__ldg(dyr + ch), dv);
+        unpack8(xc[c], xv);
+        unpack8(dc[c], dv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          xh[c][i] = (xv[i] - mean) * rstd;
-          ag[c][i] += dv[i] * xh[c][i];
+          const float xh = (xv[i] - mean) * rstd;
+          const float g = dv[i] * gm[c][i];
+          ag[c][i] += dv[i] * xh;
           ab[c][i] += dv[i];
-          g[c][i] = gamma ? dv[i] * __ldg(gamma + ch * 8 + i) : dv[i];
-          s1 += g[c][i];
-          s2 += g[c][i] * xh[c][i];
+          s1 += g;
+          s2 += g * xh;
         }
       }
     }
@@ -160,18 +198,26 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     for (int c = 0; c < MAXC; ++c) {
       const int ch = lane + 32 * c;
       if (ch < chunks) {
-        float o[8], rv[8];
+        float xv[8], dv[8], o[8], rv[8];
+        unpack8(xc[c], xv);
+        unpack8(dc[c], dv);
         if (rr) unpack8(__ldg(rr + ch), rv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          o[i] = rstd * (g[c][i] - m1 - xh[c][i] * m2);
+          const float xh = (xv[i] - mean) * rstd;
+          o[i] = rstd * (dv[i] * gm[c][i] - m1 - xh * m2);
           if (rr) o[i] += rv[i];
         }
         dxr[ch] = pack8(o);
       }
     }
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      xc[c] = xn[c];
+      dc[c] = dn[c];
+    }
   }
-  if (dgamma || dbeta) {
+  if (partial != nullptr) {
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = lane + 32 * c;
@@ -184,10 +230,23 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-      if (dgamma) atomicAdd(dgamma + i, red[i]);
-      if (dbeta) atomicAdd(dbeta + i, red[h + i]);
-    }
+    float* out = partial + static_cast<long long>(blockIdx.x) * 2 * h;
+    for (int i = threadIdx.x; i < 2 * h; i += blockDim.x) out[i] = red[i];
+  }
+}
+
+// dgamma[j] += sum_b partial[b][j], dbeta[j] += sum_b partial[b][h + j] (fixed order).
+__global__ void __launch_bounds__(256)
+ln_reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int h,
+                          float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= 2 * h) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<long long>(b) * 2 * h + j];
+  if (j < h) {
+    if (dgamma) dgamma[j] += s;
+  } else if (dbeta) {
+    dbeta[j - h] += s;
   }
 }
 
@@ -265,7 +324,7 @@ extern "C" int vmoe_layernorm_fwd(const void* x, const float* gamma, const float
   }
   const int threads = 256;
   const long long blocks = (rows * 32 + threads - 1) / threads;
-  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  const int grid = static_cast<int>(blocks < 148 * 2 ? blocks : 148 * 2);
   auto xx = static_cast<const __nv_bfloat16*>(x);
   auto yy = static_cast<__nv_bfloat16*>(y);
   const int chunks = static_cast<int>(h / 8);
@@ -279,33 +338,63 @@ extern "C" int vmoe_layernorm_fwd(const void* x, const float* gamma, const float
   return launch_status("layernorm_fwd");
 }
 
-extern "C" int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamma,
-                                  const float* mean, const float* rstd, const void* dres, void* dx,
-                                  float* dgamma, float* dbeta, int64_t rows, int64_t h,
-                                  vmoe_stream_t stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// Number of CTAs the backward kernel uses for `rows` rows (callers size the scratch with it).
+static int ln_bwd_grid(long long rows) {
+  const long long blocks = (rows * 32 + 127) / 128;
+  const long long cap = 148 * 3;
+  return static_cast<int>(blocks < cap ? blocks : cap);
+}
+
+extern "C" int64_t vmoe_layernorm_bwd_scratch_bytes(int64_t rows, int64_t h) {
+  return static_cast<int64_t>(ln_bwd_grid(rows)) * 2 * h * sizeof(float);
+}
+
+namespace vmoe {
+int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, const float* mean,
+                         const float* rstd, const void* dres, void* dx, float* dgamma,
+                         float* dbeta, float* scratch, int64_t rows, int64_t h,
+                         cudaStream_t stream) {
   if (rows == 0) return 0;
   if (h % 8 || h > 2048) {
     set_error("%s (code %d)", "layernorm: hidden size must be a multiple of 8 and <= 2048", 0);
     return -1;
   }
-  const int threads = 256;
-  const long long blocks = (rows * 32 + threads - 1) / threads;
-  const int grid = static_cast<int>(blocks < 148 * 4 ? blocks : 148 * 4);
+  const bool want = dgamma != nullptr || dbeta != nullptr;
+  if (want && scratch == nullptr) {
+    set_error("%s (code %d)", "layernorm_bwd: scratch buffer required for dgamma/dbeta", 0);
+    return -1;
+  }
+  const int threads = 128;
+  const int grid = ln_bwd_grid(rows);
   const size_t smem = 2 * h * sizeof(float);
   auto a = static_cast<const __nv_bfloat16*>(dy);
   auto b = static_cast<const __nv_bfloat16*>(x);
   auto r = static_cast<const __nv_bfloat16*>(dres);
   auto o = static_cast<__nv_bfloat16*>(dx);
+  float* part = want ? scratch : nullptr;
   const int chunks = static_cast<int>(h / 8);
 #define VMOE_LN_BWD(C) layernorm_bwd_kernel<C><<<grid, threads, smem, stream>>>( \
-      a, b, gamma, mean, rstd, r, o, dgamma, dbeta, rows, static_cast<int>(h))
+      a, b, gamma, mean, rstd, r, o, part, rows, static_cast<int>(h))
   if (chunks <= 32 * 3) VMOE_LN_BWD(3);
   else if (chunks <= 32 * 4) VMOE_LN_BWD(4);
   else if (chunks <= 32 * 5) VMOE_LN_BWD(5);
   else VMOE_LN_BWD(8);
 #undef VMOE_LN_BWD
+  if (want) {
+    const int n = static_cast<int>(2 * h);
+    ln_reduce_partials_kernel<<<(n + 255) / 256, 256, 0, stream>>>(part, grid, static_cast<int>(h),
+                                                                  dgamma, dbeta);
+  }
   return launch_status("layernorm_bwd");
+}
+}  // namespace vmoe
+
+extern "C" int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamma,
+                                  const float* mean, const float* rstd, const void* dres, void* dx,
+                                  float* dgamma, float* dbeta, float* scratch, int64_t rows,
+                                  int64_t h, vmoe_stream_t stream_) {
+  return layernorm_bwd_launch(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, rows, h,
+                              static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int vmoe_colsum_bf16(const void* x, float* out, int64_t batch, int64_t rows, int64_t n,

@@ -64,10 +64,13 @@ VMOE_API int vmoe_layernorm_fwd(const void* x, const float* gamma, const float* 
                                 float* mean, float* rstd, int64_t rows, int64_t h, float eps,
                                 vmoe_stream_t stream);
 // dx (bf16) = LayerNorm backward (+ dres if non-NULL); dgamma/dbeta (fp32) are accumulated.
+// `scratch` is global memory of vmoe_layernorm_bwd_scratch_bytes(rows, h) bytes that holds the
+// per-CTA partial sums of dgamma/dbeta (required when either is non-NULL).
+VMOE_API int64_t vmoe_layernorm_bwd_scratch_bytes(int64_t rows, int64_t h);
 VMOE_API int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamma,
                                 const float* mean, const float* rstd, const void* dres, void* dx,
-                                float* dgamma, float* dbeta, int64_t rows, int64_t h,
-                                vmoe_stream_t stream);
+                                float* dgamma, float* dbeta, float* scratch, int64_t rows,
+                                int64_t h, vmoe_stream_t stream);
 // out[b][n] (fp32) += sum over rows of bf16 x[b][rows][n]; n % 8 == 0.
 VMOE_API int vmoe_colsum_bf16(const void* x, float* out, int64_t batch, int64_t rows, int64_t n,
                               vmoe_stream_t stream);

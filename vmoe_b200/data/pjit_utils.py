@@ -63,15 +63,36 @@ def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
   stream = torch.cuda.Stream(device=device)
   pool = _PinnedPool(size)
   queue: collections.deque = collections.deque()
+  # Device-side ring: size + 1 slots per (name, shape, dtype), reused for the whole run, so the
+  # steady state allocates nothing. A slot is overwritten only after the event recorded when
+  # its consumer asked for the following batch (all work reading it is enqueued by then).
+  nslots = max(1, size) + 1
+  ring: Dict[Any, list] = {}
+  cursor: Dict[Any, int] = {}
+  released: Dict[int, torch.cuda.Event] = {}
+
+  def device_slot(name, t):
+    key = (name, tuple(t.shape), t.dtype)
+    slots = ring.setdefault(key, [])
+    i = cursor.get(key, 0)
+    if len(slots) < nslots:
+      slots.append(torch.empty(t.shape, dtype=t.dtype, device=device))
+    cursor[key] = (i + 1) % nslots
+    return slots[i % len(slots)]
 
   def enqueue(batch):
     out = {}
     with torch.cuda.stream(stream):
       for k, v in batch.items():
         t = pool.stage(k, _to_tensor(v))
-        d = t.to(device, non_blocking=True)
+        d = device_slot(k, t)
+        ev_free = released.pop(d.data_ptr(), None)
+        if ev_free is not None:
+          stream.wait_event(ev_free)
+        d.copy_(t, non_blocking=True)
         if dtypes and k in dtypes:
           d = d.to(dtypes[k])
+          d.record_stream(torch.cuda.current_stream(device))
         out[k] = d
       ev = torch.cuda.Event()
       ev.record(stream)
@@ -89,6 +110,10 @@ def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
       return
     out, ev = queue.popleft()
     torch.cuda.current_stream(device).wait_event(ev)
-    for t in out.values():
-      t.record_stream(torch.cuda.current_stream(device))
     yield out
+    done = torch.cuda.Event()
+    done.record(torch.cuda.current_stream(device))
+    for slots in ring.values():
+      for t in slots:
+        if any(t.data_ptr() == o.data_ptr() for o in out.values()):
+          released[t.data_ptr()] = done

@@ -44,12 +44,17 @@ class _LayerNormFn(torch.autograd.Function):
     dx = torch.empty_like(x2)
     dgamma = torch.zeros(h, dtype=torch.float32, device=dy.device) if weight is not None else None
     dbeta = torch.zeros(h, dtype=torch.float32, device=dy.device) if ctx.has_bias else None
-    rc = _lib.lib().vmoe_layernorm_bwd(
+    lib = _lib.lib()
+    lib.vmoe_layernorm_bwd_scratch_bytes.restype = ctypes.c_int64
+    nbytes = lib.vmoe_layernorm_bwd_scratch_bytes(ctypes.c_int64(rows), ctypes.c_int64(h))
+    scratch = torch.empty(max(int(nbytes) // 4, 1), dtype=torch.float32, device=dy.device)
+    rc = lib.vmoe_layernorm_bwd(
         _vp(dy2.data_ptr()), _vp(x2.data_ptr()), _vp(_lib.ptr(weight)), _vp(mean.data_ptr()),
         _vp(rstd.data_ptr()), _vp(None), _vp(dx.data_ptr()), _vp(_lib.ptr(dgamma)),
-        _vp(_lib.ptr(dbeta)), ctypes.c_int64(rows), ctypes.c_int64(h), _vp(_lib.stream_ptr()))
+        _vp(_lib.ptr(dbeta)), _vp(scratch.data_ptr()), ctypes.c_int64(rows), ctypes.c_int64(h),
+        _vp(_lib.stream_ptr()))
     _lib.check(rc, "vmoe_layernorm_bwd")
-    _lib.count_launch()
+    _lib.count_launch(2)
     return dx.reshape(ctx.shape), dgamma, dbeta, None
 
 
