@@ -1,0 +1,123 @@
+"""Micro-benchmarks of single kernels on ViT-B/16 training shapes (one GPU).
+
+  python -m vmoe_b200.ops.bench_kernels <case> [--rows 100864] [--iters 10]
+
+Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with residual),
+``layernorm`` (forward and backward), ``attention`` (packed-QKV forward and backward),
+``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward).
+Every case runs one warm-up pass, then times ``iters`` passes with CUDA events; inputs are
+larger than the L2 cache. The same commands are the workloads of the profiler summaries kept
+under ``profiles/``.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def _timed(fn, iters):
+  fn()
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(iters):
+    fn()
+  e1.record()
+  torch.cuda.synchronize()
+  return e0.elapsed_time(e1) * 1e3 / iters  # microseconds
+
+
+def gemm_dense(rows: int, iters: int):
+  from vmoe_b200.ops import gemm as G
+  dev = "cuda"
+  x = torch.randn(rows, 768, device=dev).bfloat16()
+  wqkv = torch.randn(2304, 768, device=dev).bfloat16()
+  bqkv = torch.randn(2304, device=dev)
+  w1 = torch.randn(3072, 768, device=dev).bfloat16()
+  b1 = torch.randn(3072, device=dev)
+  wo = torch.randn(768, 768, device=dev).bfloat16()
+  bo = torch.randn(768, device=dev)
+  res = torch.randn(rows, 768, device=dev).bfloat16()
+  pre = torch.empty(rows, 3072, device=dev, dtype=torch.bfloat16)
+  cases = {
+      "qkv": (lambda: G.gemm(x, wqkv, bias=bqkv), 2 * rows * 768 * 2304),
+      "fc1_gelu": (lambda: G.gemm(x, w1, bias=b1, act=G.ACT_GELU, out_pre=pre),
+                   2 * rows * 768 * 3072),
+      "out_proj_residual": (lambda: G.gemm(x, wo, bias=bo, residual=res), 2 * rows * 768 * 768),
+  }
+  for name, (fn, flops) in cases.items():
+    us = _timed(fn, iters)
+    print(f"{name}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+
+
+def layernorm(rows: int, iters: int):
+  from vmoe_b200 import ops
+  x = torch.randn(rows, 768, device="cuda").bfloat16().requires_grad_()
+  w = torch.ones(768, device="cuda", requires_grad=True)
+  b = torch.zeros(768, device="cuda", requires_grad=True)
+  y = ops.layer_norm(x, w, b, 1e-6)
+  g = torch.randn_like(y)
+  us_f = _timed(lambda: ops.layer_norm(x, w, b, 1e-6), iters)
+
+  def both():
+    ops.layer_norm(x, w, b, 1e-6).backward(g)
+
+  us_fb = _timed(both, iters)
+  nbytes = rows * 768 * 2
+  print(f"layernorm fwd: {us_f:.1f} us ({2 * nbytes / us_f / 1e3:.0f} GB/s); "
+        f"fwd+bwd: {us_fb:.1f} us")
+
+
+def attention(rows: int, iters: int):
+  from vmoe_b200 import ops
+  batch = max(rows // 197, 1)
+  qkv = torch.randn(batch, 197, 3 * 768, device="cuda").bfloat16().requires_grad_()
+  out = ops.attention_packed(qkv, 12)
+  g = torch.randn_like(out)
+  us_f = _timed(lambda: ops.attention_packed(qkv, 12), iters)
+
+  def both():
+    ops.attention_packed(qkv, 12).backward(g)
+
+  us_fb = _timed(both, iters)
+  flops = 4 * batch * 12 * 197 * 197 * 64
+  print(f"attention fwd: {us_f:.1f} us ({flops / us_f / 1e6:.0f} TFLOP/s useful); "
+        f"fwd+bwd: {us_fb:.1f} us")
+
+
+def router(rows: int, iters: int):
+  from vmoe_b200.models import routing
+  groups = 32
+  x = torch.randn(groups, rows // groups, 768, device="cuda").bfloat16().requires_grad_()
+  r = routing.NoisyTopExpertsPerItemRouter(
+      num_experts=8, hidden_size=768, num_selected_experts=2, noise_std=1.0,
+      importance_loss_weight=0.005, load_loss_weight=0.005,
+      dispatcher=dict(name="einsum", capacity_factor=1.05, batch_priority=True)).cuda()
+  r.train()
+
+  def fwd():
+    return r._compute_gates_softmax_and_metrics(x, 8)
+
+  def both():
+    gates, metrics = fwd()
+    (gates.square().sum() + metrics["auxiliary_loss"].sum()).backward()
+
+  print(f"router fwd: {_timed(fwd, iters):.1f} us; fwd+bwd: {_timed(both, iters):.1f} us")
+
+
+CASES = {"gemm_dense": gemm_dense, "layernorm": layernorm, "attention": attention,
+         "router": router}
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("case", choices=sorted(CASES))
+  ap.add_argument("--rows", type=int, default=100864)
+  ap.add_argument("--iters", type=int, default=10)
+  args = ap.parse_args()
+  CASES[args.case](args.rows, args.iters)
+
+
+if __name__ == "__main__":
+  main()
