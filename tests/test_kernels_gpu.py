@@ -184,3 +184,46 @@ def test_packed_attention(b, t, h):
   _close(qkv.grad[:, :, 2], ref_in.grad[:, :, 2], 3e-2)  # dV
   _close(qkv.grad[:, :, 1], ref_in.grad[:, :, 1], 3e-2)  # dK
   _close(qkv.grad[:, :, 0], ref_in.grad[:, :, 0], 3e-2)  # dQ
+
+
+@pytest.mark.parametrize("g,s,e,k,noisy", [(4, 197, 8, 2, True), (3, 50, 8, 1, False),
+                                          (2, 333, 32, 3, True), (5, 7, 4, 2, True)])
+def test_router_stats_kernels_match_torch(g, s, e, k, noisy):
+  from vmoe_b200.models import routing
+  torch.manual_seed(0)
+  r = routing.NoisyTopExpertsPerItemRouter(
+      num_experts=e, hidden_size=16, num_selected_experts=k, noise_std=1.0 if noisy else 0.0,
+      gshard_loss_weight=0.3, importance_loss_weight=0.7, load_loss_weight=0.5,
+      dispatcher=dict(name="einsum", capacity_factor=1.0, batch_priority=False)).to(DEV)
+  r.train()
+  logits = (torch.randn(g, s, e, device=DEV) * 2).requires_grad_()
+  noise = torch.randn(g, s, e, device=DEV)
+  probe = torch.randn(g, s, e, device=DEV)
+  gates, metrics = r._gates_and_metrics_from_logits(logits, e, noise=noise)
+  (gates * probe).sum().add(metrics["auxiliary_loss"].sum() * 10).backward()
+  l2 = logits.detach().clone().requires_grad_()
+  with ops.use_cuda_kernels(False):
+    gates2, metrics2 = r._gates_and_metrics_from_logits(l2, e, noise=noise)
+  (gates2 * probe).sum().add(metrics2["auxiliary_loss"].sum() * 10).backward()
+  _close(gates, gates2, 1e-5)
+  for key in metrics2:
+    _close(metrics[key], metrics2[key], 2e-4)
+  _close(logits.grad, l2.grad, 2e-4)
+
+
+def test_gating_logits_gemm():
+  from vmoe_b200.ops import router_ops
+  torch.manual_seed(0)
+  x = torch.randn(6, 197, 768, device=DEV).bfloat16().requires_grad_()
+  w = (torch.randn(8, 768, device=DEV) * 0.05).requires_grad_()
+  out = router_ops.gating_logits(x, w)
+  assert out.dtype == torch.float32 and out.shape == (6, 197, 8)
+  probe = torch.randn_like(out)
+  (out * probe).sum().backward()
+  x2 = x.detach().float().requires_grad_()
+  w2 = w.detach().bfloat16().float().requires_grad_()
+  out2 = x2 @ w2.t()
+  (out2 * probe.bfloat16().float()).sum().backward()
+  _close(out, out2, 1e-3)
+  _close(x.grad, x2.grad, 1e-2)
+  _close(w.grad, w2.grad, 1e-2)

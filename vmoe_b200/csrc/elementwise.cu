@@ -235,18 +235,29 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
-// dgamma[j] += sum_b partial[b][j], dbeta[j] += sum_b partial[b][h + j] (fixed order).
+// dgamma[j] += sum_b partial[b][j], dbeta[j] += sum_b partial[b][h + j]. Block = 32 columns x
+// 8 row groups; every thread adds a strided subset of the rows in a fixed order and the eight
+// partial results are combined through shared memory, also in a fixed order.
 __global__ void __launch_bounds__(256)
 ln_reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int h,
                           float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= 2 * h) return;
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<long long>(b) * 2 * h + j];
-  if (j < h) {
-    if (dgamma) dgamma[j] += s;
-  } else if (dbeta) {
-    dbeta[j - h] += s;
+  if (j < 2 * h)
+    for (int b = ty; b < nblocks; b += 8) s += partial[static_cast<long long>(b) * 2 * h + j];
+  part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < 2 * h) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += part[r][tx];
+    if (j < h) {
+      if (dgamma) dgamma[j] += t;
+    } else if (dbeta) {
+      dbeta[j - h] += t;
+    }
   }
 }
 
@@ -382,7 +393,7 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
 #undef VMOE_LN_BWD
   if (want) {
     const int n = static_cast<int>(2 * h);
-    ln_reduce_partials_kernel<<<(n + 255) / 256, 256, 0, stream>>>(part, grid, static_cast<int>(h),
+    ln_reduce_partials_kernel<<<(n + 31) / 32, 256, 0, stream>>>(part, grid, static_cast<int>(h),
                                                                   dgamma, dbeta);
   }
   return launch_status("layernorm_bwd");

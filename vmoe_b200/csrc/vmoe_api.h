@@ -169,6 +169,21 @@ VMOE_API int vmoe_signal(uint32_t* flag, uint32_t value, vmoe_stream_t stream);
 VMOE_API int vmoe_wait_counters(const uint32_t* counters, int32_t n, uint32_t target,
                                 uint32_t* status, int64_t limit_cycles, vmoe_stream_t stream);
 
+// Noisy Top-K router statistics. logits/noise/gates_out: [tokens][E] fp32 (noise NULL = no
+// noise, no load loss); sums: [G][4][E] scratch (importance, load, top-1 counts, gate sums);
+// losses: [G][3] = importance, load, gshard; coef: [G][3][E] = d loss / d sum, kept for backward.
+VMOE_API int vmoe_router_stats_fwd(const float* logits, const float* noise, float* gates_out,
+                                   float* sums, float* losses, float* coef, int64_t tokens,
+                                   int64_t group_size, int num_experts, float noise_std, int k,
+                                   vmoe_stream_t stream);
+// d_logits (fp32, may be NULL) and d_logits_bf16 (row stride ld_bf16, may be NULL) from the
+// gradients of gates_out (d_gates, may be NULL) and of the three losses (d_losses [G][3]).
+VMOE_API int vmoe_router_stats_bwd(const float* logits, const float* noise, const float* d_gates,
+                                   const float* d_losses, const float* coef, float* d_logits,
+                                   void* d_logits_bf16, int64_t ld_bf16, int64_t tokens,
+                                   int64_t group_size, int num_experts, float noise_std, int k,
+                                   vmoe_stream_t stream);
+
 // Last error text of the calling thread ("" if none).
 VMOE_API const char* vmoe_last_error(void);
 

@@ -71,6 +71,9 @@ class _RouterBase(nn.Module):
     # Gating runs in fp32 on bf16 activations too: logits feed a softmax and a top-k whose
     # ties/ordering should not depend on bf16 rounding.
     if dtype == torch.bfloat16:
+      from vmoe_b200.ops import router_ops
+      if router_ops.gating_logits_supported(inputs, self.dense.weight):
+        return router_ops.gating_logits(inputs, self.dense.weight)
       dtype = torch.float32
     return torch.matmul(inputs.to(dtype), self.dense.weight.to(dtype).t())
 
@@ -110,6 +113,9 @@ class NoisyTopExpertsPerItemRouter(_RouterBase):
 
   def _gates_and_metrics_from_logits(self, logits: Tensor, num_experts: int, noise=None):
     """``logits (G, S, E)`` -> (softmax gates used for dispatch, per-group metrics)."""
+    from vmoe_b200.ops import router_ops
+    if router_ops.router_stats_supported(logits):
+      return self._fused_gates_and_metrics(logits, num_experts, noise)
     gates = torch.softmax(logits, dim=-1)
     importance_loss = self._importance_auxiliary_loss(gates)
     if self.is_deterministic() or self.noise_std == 0.0:
@@ -139,6 +145,27 @@ class NoisyTopExpertsPerItemRouter(_RouterBase):
         "load_loss": load_loss,
     }
     return gates_noisy, metrics
+
+  def _fused_gates_and_metrics(self, logits: Tensor, num_experts: int, noise=None):
+    """Same contract as the PyTorch branch of ``_gates_and_metrics_from_logits``, evaluated by
+    the router-statistics kernels."""
+    from vmoe_b200.ops import router_ops
+    noisy = not (self.is_deterministic() or self.noise_std == 0.0)
+    noise_std = self.noise_std / num_experts
+    if noisy and noise is None:
+      noise = (self.injected_noise.to(logits) if self.injected_noise is not None
+               else torch.randn_like(logits))
+    gates, importance_loss, load_loss, gshard_loss = router_ops.router_stats(
+        logits, noise if noisy else None, noise_std if noisy else 1.0,
+        self.num_selected_experts)
+    pairs = [(self.gshard_loss_weight, gshard_loss),
+             (self.importance_loss_weight, importance_loss)]
+    metrics = {"gshard_loss": gshard_loss, "importance_loss": importance_loss}
+    if noisy:
+      pairs.append((self.load_loss_weight, load_loss))
+      metrics["load_loss"] = load_loss
+    metrics["auxiliary_loss"] = _weighted_sum(*pairs)
+    return gates, metrics
 
   def _create_dispatcher(self, gates: Tensor, inputs: Optional[Tensor] = None):
     kwargs = dict(self.dispatcher_kwargs)
