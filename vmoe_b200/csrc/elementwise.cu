@@ -148,13 +148,11 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
                      __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, long long rows,
                      int h) {
-  extern __shared__ float red[];  // [2][h]
+  extern __shared__ float red[];  // [4 warps][2][h]
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const int chunks = h >> 3;
-  for (int i = threadIdx.x; i < 2 * h; i += blockDim.x) red[i] = 0.f;
-  __syncthreads();
   float gm[MAXC][8];
   ln_load_affine<MAXC>(gamma, lane, chunks, 1.0f, gm);
   float ag[MAXC][8], ab[MAXC][8];
@@ -218,20 +216,24 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
     }
   }
   if (partial != nullptr) {
+    // Each warp stores its sums in its own slice; the four slices are then added in a fixed
+    // order, so the result does not depend on warp scheduling.
+    float* mine = red + (threadIdx.x >> 5) * 2 * h;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = lane + 32 * c;
       if (ch < chunks) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          atomicAdd(&red[ch * 8 + i], ag[c][i]);
-          atomicAdd(&red[h + ch * 8 + i], ab[c][i]);
+          mine[ch * 8 + i] = ag[c][i];
+          mine[h + ch * 8 + i] = ab[c][i];
         }
       }
     }
     __syncthreads();
     float* out = partial + static_cast<long long>(blockIdx.x) * 2 * h;
-    for (int i = threadIdx.x; i < 2 * h; i += blockDim.x) out[i] = red[i];
+    for (int i = threadIdx.x; i < 2 * h; i += blockDim.x)
+      out[i] = (red[i] + red[2 * h + i]) + (red[4 * h + i] + red[6 * h + i]);
   }
 }
 
@@ -377,7 +379,7 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
   }
   const int threads = 128;
   const int grid = ln_bwd_grid(rows);
-  const size_t smem = 2 * h * sizeof(float);
+  const size_t smem = 4 * 2 * h * sizeof(float);  // one slice per warp (threads / 32 = 4)
   auto a = static_cast<const __nv_bfloat16*>(dy);
   auto b = static_cast<const __nv_bfloat16*>(x);
   auto r = static_cast<const __nv_bfloat16*>(dres);
@@ -389,7 +391,11 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
   if (chunks <= 32 * 3) VMOE_LN_BWD(3);
   else if (chunks <= 32 * 4) VMOE_LN_BWD(4);
   else if (chunks <= 32 * 5) VMOE_LN_BWD(5);
-  else VMOE_LN_BWD(8);
+  else {
+    cudaFuncSetAttribute(layernorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         4 * 2 * 2048 * static_cast<int>(sizeof(float)));
+    VMOE_LN_BWD(8);
+  }
 #undef VMOE_LN_BWD
   if (want) {
     const int n = static_cast<int>(2 * h);
