@@ -461,3 +461,52 @@ extern "C" int vmoe_patchify(const void* img, int32_t img_is_bf16, void* out, in
         static_cast<int>(pw), static_cast<int>(gh), static_cast<int>(gw));
   return launch_status("patchify");
 }
+
+// ------------------------------------------------------------------ no-allocation LayerNorm backward
+// Same computation as vmoe_layernorm_bwd, but the per-CTA partial sums of dgamma / dbeta live in
+// the file-scope device array below instead of a caller-provided buffer, so the call allocates
+// nothing. The array holds kLnStaticMaxCtas rows of 2 * kLnStaticMaxHidden floats (3.5 MiB);
+// larger hidden sizes are rejected.
+namespace {
+constexpr int kLnStaticMaxCtas = 148 * 3;     // grid cap of the backward kernel
+constexpr int kLnStaticMaxHidden = 1024;
+constexpr int kLnStaticMaxDevices = 64;
+static __device__ __align__(256) float g_ln_bwd_scratch[kLnStaticMaxCtas * 2 * kLnStaticMaxHidden];
+float* g_ln_bwd_scratch_ptr[kLnStaticMaxDevices] = {};
+}  // namespace
+
+extern "C" int vmoe_layernorm_bwd_static(const void* dy, const void* x, const float* gamma,
+                                         const float* mean, const float* rstd, const void* dres,
+                                         void* dx, float* dgamma, float* dbeta, int64_t rows,
+                                         int64_t h, vmoe_stream_t stream_) {
+  if (h > kLnStaticMaxHidden) {
+    set_error("%s (code %d)",
+              "layernorm_bwd_static: hidden size above the static scratch limit of 1024",
+              static_cast<int>(h));
+    return -1;
+  }
+  if (ln_bwd_grid(rows) > kLnStaticMaxCtas) {
+    set_error("%s (code %d)", "layernorm_bwd_static: grid above the static scratch limit", 0);
+    return -1;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kLnStaticMaxDevices) {
+    set_error("%s (code %d)", "layernorm_bwd_static: cannot identify the current device",
+              static_cast<int>(e));
+    return -5;
+  }
+  if (g_ln_bwd_scratch_ptr[dev] == nullptr) {
+    // One-time set-up per device: resolve the device address of the static array.
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_ln_bwd_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
+      return -5;
+    }
+    g_ln_bwd_scratch_ptr[dev] = ptr;
+  }
+  return layernorm_bwd_launch(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta,
+                              g_ln_bwd_scratch_ptr[dev], rows, h,
+                              static_cast<cudaStream_t>(stream_));
+}

@@ -71,6 +71,21 @@ VMOE_API int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamm
                                 const float* mean, const float* rstd, const void* dres, void* dx,
                                 float* dgamma, float* dbeta, float* scratch, int64_t rows,
                                 int64_t h, vmoe_stream_t stream);
+// No-allocation variant of vmoe_layernorm_bwd (this entry point has no counterpart in the
+// reference, which leaves all memory management to XLA). The partial sums of dgamma / dbeta go
+// to a static device array inside the library (3.5 MiB, hidden sizes up to 1024) instead of a
+// caller-provided scratch buffer, and the call invokes no allocating routine.
+//  * The first call on each device resolves the array's device address (a host-side set-up
+//    step); make that call before any stream capture.
+//  * All calls on a device share the one array. It keeps the contents of the last call; nothing
+//    in it has to be zero on entry, because every launch overwrites the rows it later reads.
+//  * Calls that overlap in time on one device (different streams or threads) race on the array;
+//    serialise them.
+//  * Returns -1 with a message in vmoe_last_error() when h > 1024.
+VMOE_API int vmoe_layernorm_bwd_static(const void* dy, const void* x, const float* gamma,
+                                       const float* mean, const float* rstd, const void* dres,
+                                       void* dx, float* dgamma, float* dbeta, int64_t rows,
+                                       int64_t h, vmoe_stream_t stream);
 // out[b][n] (fp32) += sum over rows of bf16 x[b][rows][n]; n % 8 == 0.
 VMOE_API int vmoe_colsum_bf16(const void* x, float* out, int64_t batch, int64_t rows, int64_t n,
                               vmoe_stream_t stream);
