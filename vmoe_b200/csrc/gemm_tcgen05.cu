@@ -7,6 +7,12 @@
 // tile's columns). bf16 outputs leave through 64B-swizzled shared-memory staging and TMA
 // stores, which clip rows and columns that fall outside the matrix.
 //
+// Two instantiations: one CTA per 128 x 256 tile (cta_group::1), and CTA pairs launched as
+// 2-CTA clusters that share one 256 x 256 tile (cta_group::2). In a pair each CTA stages its own
+// 128 rows of A and one half (128 columns) of B, the even CTA issues the MMAs for both, and
+// each CTA's TMEM receives the accumulator rows of its own A tile. Per MMA every SM then moves
+// 8 KB instead of 12 KB through its shared memory, which is what bounds the single-CTA tile.
+//
 // This one kernel covers every dense and expert matmul of the model: forward (x W^T), dgrad
 // (dy W, B read MN-major) and wgrad (dy^T x, both operands MN-major, split-K with fp32
 // atomics), batched over experts through the third TMA coordinate. It replaces the matmuls
@@ -16,6 +22,7 @@
 #include <cudaTypedefs.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "ptx_sm100.cuh"
@@ -37,8 +44,12 @@ constexpr int EPI_WARPS = 8;                // two per TMEM lane quadrant, 128 c
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int EPI_CHUNK_BYTES = 32 * 32 * 2;  // 32 rows x 32 bf16 columns, 64 B swizzled rows
 constexpr int EPI_STAGE_BYTES = EPI_WARPS * 2 * EPI_CHUNK_BYTES;  // C and C2 staging per warp
+constexpr int STAGES_PAIR = 6;                   // pair mode stages half of B per CTA
+constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2;  // 16 KiB
 constexpr int SMEM_BYTES =
     STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_STAGE_BYTES + 1024 /*align*/ + 256;
+static_assert(STAGES_PAIR * (A_STAGE_BYTES + B_HALF_BYTES) == STAGES * (A_STAGE_BYTES + B_STAGE_BYTES),
+              "both modes use the same shared-memory budget");
 
 struct GemmParams {
   void* C;
@@ -100,6 +111,7 @@ __device__ __forceinline__ void warp_transpose_reduce(float (&v)[32], int lane) 
   }
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_c2,
@@ -107,31 +119,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  constexpr int NSTAGE = PAIR ? STAGES_PAIR : STAGES;
+  constexpr int BSTAGE = PAIR ? B_HALF_BYTES : B_STAGE_BYTES;  // B bytes this CTA stages
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;                   // N rows of B this CTA stages
+  constexpr int TM = PAIR ? 2 * BM : BM;                       // rows of one tile
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint8_t* sEpi = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  uint8_t* sB = smem + NSTAGE * A_STAGE_BYTES;
+  uint8_t* sEpi = smem + NSTAGE * (A_STAGE_BYTES + BSTAGE);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_STAGE_BYTES);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
+  // Pair mode: rank 0 (the even CTA) leads. `cta` / `ncta` index tiles per CTA or per pair.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int ncta = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   const uint32_t bar_full = smem_u32(bars);
-  const uint32_t bar_empty = smem_u32(bars + STAGES);
-  const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES);
-  const uint32_t bar_tempty = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t bar_empty = smem_u32(bars + NSTAGE);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * NSTAGE);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * NSTAGE + 2);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, EPI_WARPS);  // one arrival per epilogue warp
+      // one arrival per epilogue warp (of both CTAs in pair mode; only the leader's is used)
+      mbar_init(bar_tempty + 8 * s, PAIR ? 2 * EPI_WARPS : EPI_WARPS);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -142,15 +163,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  // Pair mode: the peer's barriers must be initialised before anything arrives on them.
+  if (PAIR) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_m = (p.M + BM - 1) / BM;
+  const int num_m = (p.M + TM - 1) / TM;
+  const int num_m128 = (p.M + BM - 1) / BM;
+  const int mt_rot = PAIR ? p.mt_offset / 2 : p.mt_offset;
   const int num_n = (p.N + BN - 1) / BN;
   const int k_tiles = (p.K + BK - 1) / BK;
   const int k_per_split = (k_tiles + p.split_k - 1) / p.split_k;
@@ -162,17 +192,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, p.mt_offset);
-        const int m0 = t.mt * BM, n0 = t.nt * BN;
+      // Pair mode: completion bytes of both CTAs are counted on the leader's full barrier.
+      const uint32_t full_base = PAIR ? mapa_shared(bar_full, 0) : bar_full;
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, mt_rot);
+        const int m0 = t.mt * TM + static_cast<int>(rank) * BM;
+        const int n0 = t.nt * BN + static_cast<int>(rank) * B_ROWS;  // this CTA's rows of B
         const int kt0 = t.ks * k_per_split;
         const int kt1 = min(k_tiles, kt0 + k_per_split);
-        if (p.a_ready != nullptr && kt0 < kt1) {
+        if (p.a_ready != nullptr && kt0 < kt1 && m0 < p.M) {
           // Rows of this A tile are produced by another kernel (possibly on a peer GPU) that
           // adds the number of rows it wrote to a counter, release at system scope.
           const unsigned rows = static_cast<unsigned>(min(BM, p.M - m0));
           const unsigned want = p.a_ready_epoch * rows;
-          const unsigned* flag = p.a_ready + (static_cast<long long>(t.b) * num_m + t.mt);
+          const unsigned* flag = p.a_ready + (static_cast<long long>(t.b) * num_m128 + m0 / BM);
           const long long t0 = clock64();
           while (static_cast<int>(ld_acquire_sys(flag) - want) < 0) {
             if (*abort_flag || clock64() - t0 > kWaitLimitCycles) {
@@ -192,26 +225,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             ok = false;
             break;
           }
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
+          const uint32_t full = full_base + 8 * stage;
+          if (!PAIR) {
+            mbar_expect_tx(full, A_STAGE_BYTES + BSTAGE);
+          } else if (rank == 0) {
+            mbar_expect_tx(bar_full + 8 * stage, 2 * (A_STAGE_BYTES + BSTAGE));
+          }
           const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
+          const uint32_t b_dst = smem_u32(sB + stage * BSTAGE);
           const int k0 = kt * BK;
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) {
+            if (PAIR) {
+              tma_load_3d_pair(dst, map, full, c0, c1, t.b);
+            } else {
+              tma_load_3d(dst, map, full, c0, c1, t.b);
+            }
+          };
           if (!p.a_mn_major) {
-            tma_load_3d(a_dst, &tma_a, full, k0, m0, t.b);
+            load(a_dst, &tma_a, k0, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              tma_load_3d(a_dst + j * CHUNK_BYTES, &tma_a, full, m0 + 64 * j, k0, t.b);
+            for (int j = 0; j < BM / 64; ++j) load(a_dst + j * CHUNK_BYTES, &tma_a, m0 + 64 * j, k0);
           }
           if (!p.b_mn_major) {
-            tma_load_3d(b_dst, &tma_b, full, k0, n0, t.b);
+            load(b_dst, &tma_b, k0, n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(b_dst + j * CHUNK_BYTES, &tma_b, full, n0 + 64 * j, k0, t.b);
+            for (int j = 0; j < B_ROWS / 64; ++j)
+              load(b_dst + j * CHUNK_BYTES, &tma_b, n0 + 64 * j, k0);
           }
-          if (++stage == STAGES) {
+          if (++stage == NSTAGE) {
             stage = 0;
             phase ^= 1;
           }
@@ -225,8 +268,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_bf16(TM, BN, p.a_mn_major, p.b_mn_major);
       // K-major: 8-row groups 1024 B apart, 32 B per UMMA_K step inside the swizzle row.
       // MN-major: 64-element chunks CHUNK_BYTES apart (LBO), 8-row K groups 1024 B apart
       // (SBO), 16 K rows = 2048 B per UMMA_K step.
@@ -236,8 +279,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, p.mt_offset);
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++local) {
+        const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, mt_rot);
         const int kt0 = t.ks * k_per_split;
         const int kt1 = min(k_tiles, kt0 + k_per_split);
         const int slot = local & 1;
@@ -256,21 +299,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * BSTAGE);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = umma_smem_desc(a_addr + k * a_step, a_lbo, 1024);
             const uint64_t bdesc = umma_smem_desc(b_addr + k * b_step, b_lbo, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kt > kt0 || k > 0) ? 1u : 0u);
+            if (PAIR) {
+              umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kt > kt0 || k > 0) ? 1u : 0u);
+            } else {
+              umma_bf16(d_tmem, adesc, bdesc, idesc, (kt > kt0 || k > 0) ? 1u : 0u);
+            }
           }
-          umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs retire
-          if (++stage == STAGES) {
+          // Frees the smem stage (in both CTAs of a pair) once these MMAs retire.
+          if (PAIR) {
+            umma_commit_pair(bar_empty + 8 * stage, 3);
+          } else {
+            umma_commit(bar_empty + 8 * stage);
+          }
+          if (++stage == NSTAGE) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(bar_tfull + 8 * slot);  // accumulator complete -> epilogue
+        // accumulator complete -> epilogue (of both CTAs in pair mode)
+        if (PAIR) {
+          umma_commit_pair(bar_tfull + 8 * slot, 3);
+        } else {
+          umma_commit(bar_tfull + 8 * slot);
+        }
       }
     }
   } else {
@@ -284,8 +341,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const uint32_t st_xor = (static_cast<uint32_t>(lane) >> 1) & 3u;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-      const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, p.mt_offset);
+    const uint32_t tempty_base = PAIR ? mapa_shared(bar_tempty, 0) : bar_tempty;
+    for (int tile = cta; tile < num_tiles && ok; tile += ncta, ++local) {
+      const TileCoord t = decode_tile(tile, num_m, num_n, p.split_k, mt_rot);
       const int kt0 = t.ks * k_per_split;
       const int kt1 = min(k_tiles, kt0 + k_per_split);
       const int slot = local & 1;
@@ -298,7 +356,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_after();
       const bool empty_k = kt0 >= kt1;  // a split with no K tiles contributes nothing
-      const int row0 = t.mt * BM + quad * 32;
+      const int row0 = t.mt * TM + static_cast<int>(rank) * BM + quad * 32;
       const int row = row0 + lane;
       const bool row_ok = row < p.M;
       const int n0 = t.nt * BN;
@@ -393,14 +451,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           // Fused forward: C = gelu(v) and C2 = gelu'(v) share one tanh.
           float a[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float x = v[i];
-            const float x2 = x * x;
-            const float tt = tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x2));
-            const float hp = 0.5f * (1.0f + tt);
-            a[i] = x * hp;
-            v[i] = hp + 0.5f * x * (1.0f - tt * tt) * (0.7978845608028654f * (1.0f + 0.134145f * x2));
-          }
+          for (int i = 0; i < 32; i += 2)
+            gelu_and_grad_pair(v[i], v[i + 1], a[i], a[i + 1], v[i], v[i + 1]);
           // v now holds gelu' (stored to C2 below); a holds the activation (restored after).
           if (p.tma_store) {
 #pragma unroll
@@ -452,7 +504,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         if (p.act == 1 && !(p.C2 && p.c2_gelu_grad)) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+          for (int i = 0; i < 32; i += 2) gelu_pair(v[i], v[i + 1], v[i], v[i + 1]);
         }
         if (p.gelu_pre && row_ok) {
           const __nv_bfloat16* pre = p.gelu_pre + static_cast<long long>(t.b) * p.r_batch_stride +
@@ -475,14 +527,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 v[8 * i + 6] *= f3.x;
                 v[8 * i + 7] *= f3.y;
               } else {
-                v[8 * i + 0] *= gelu_tanh_grad(f0.x);
-                v[8 * i + 1] *= gelu_tanh_grad(f0.y);
-                v[8 * i + 2] *= gelu_tanh_grad(f1.x);
-                v[8 * i + 3] *= gelu_tanh_grad(f1.y);
-                v[8 * i + 4] *= gelu_tanh_grad(f2.x);
-                v[8 * i + 5] *= gelu_tanh_grad(f2.y);
-                v[8 * i + 6] *= gelu_tanh_grad(f3.x);
-                v[8 * i + 7] *= gelu_tanh_grad(f3.y);
+                float d0, d1;
+                gelu_grad_pair(f0.x, f0.y, d0, d1);
+                v[8 * i + 0] *= d0;
+                v[8 * i + 1] *= d1;
+                gelu_grad_pair(f1.x, f1.y, d0, d1);
+                v[8 * i + 2] *= d0;
+                v[8 * i + 3] *= d1;
+                gelu_grad_pair(f2.x, f2.y, d0, d1);
+                v[8 * i + 4] *= d0;
+                v[8 * i + 5] *= d1;
+                gelu_grad_pair(f3.x, f3.y, d0, d1);
+                v[8 * i + 6] *= d0;
+                v[8 * i + 7] *= d1;
               }
             }
           } else {
@@ -586,7 +643,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * slot);
+      if (lane == 0) {
+        if (PAIR) {
+          mbar_arrive_cluster(tempty_base + 8 * slot);
+        } else {
+          mbar_arrive(bar_tempty + 8 * slot);
+        }
+      }
     }
     // Outstanding TMA stores must finish reading shared memory before the CTA exits.
     if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -594,9 +657,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {
+    // Neither CTA may free TMEM or exit while its peer can still touch its barriers or TMEM.
+    cluster_sync_all();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) {
+      tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    } else {
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
   }
 }
 
@@ -644,6 +715,57 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     set_error("%s (code %d)", "split_k / atomic output needs c_fp32 and c_atomic", 0);
     return -1;
   }
+  static int sm_count = 0;
+  static int max_pairs = 0;  // CTA pairs (2-CTA clusters) that can be resident at once
+  static bool attr_set = false;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
+      return -4;
+    }
+    cudaLaunchConfig_t probe;
+    memset(&probe, 0, sizeof(probe));
+    cudaLaunchAttribute pattr;
+    pattr.id = cudaLaunchAttributeClusterDimension;
+    pattr.val.clusterDim.x = 2;
+    pattr.val.clusterDim.y = 1;
+    pattr.val.clusterDim.z = 1;
+    probe.gridDim = dim3(static_cast<unsigned>(sm_count & ~1));
+    probe.blockDim = dim3(GEMM_THREADS);
+    probe.dynamicSmemBytes = SMEM_BYTES;
+    probe.attrs = &pattr;
+    probe.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel<true>, &probe) != cudaSuccess) {
+      cudaGetLastError();
+      clusters = 0;
+    }
+    max_pairs = clusters;
+    attr_set = true;
+  }
+  const char* env_pair = getenv("VMOE_B200_GEMM_PAIR");  // "0" / "1" override for experiments
+  int pair_mode = a->cta_pair;
+  if (pair_mode == 0 && env_pair != nullptr) pair_mode = env_pair[0] == '0' ? 1 : 2;
+  bool pair = false;
+  if (max_pairs > 0) {
+    if (pair_mode == 2) {
+      pair = true;
+    } else if (pair_mode == 0) {
+      // Pairs pay off once there is at least one 256 x 256 tile per pair of SMs.
+      const long long pair_tiles = a->batch * ((a->M + 2 * BM - 1) / (2 * BM)) *
+                                   ((a->N + BN - 1) / BN) * (a->split_k > 1 ? a->split_k : 1);
+      pair = a->M >= 2 * BM && a->N >= BN / 2 && pair_tiles >= max_pairs / 2 &&
+             a->a_ready == nullptr;  // tiles gated by peer arrival counters stay one per CTA
+    }
+  }
   CUtensorMap ma, mb;
   int rc;
   if (!a->a_mn_major)
@@ -652,7 +774,8 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     rc = make_bf16_map(&ma, a->A, a->M, a->K, a->batch, a->lda, a->a_batch_stride, BK);
   if (rc) return rc;
   if (!a->b_mn_major)
-    rc = make_bf16_map(&mb, a->B, a->K, a->N, a->batch, a->ldb, a->b_batch_stride, BN);
+    rc = make_bf16_map(&mb, a->B, a->K, a->N, a->batch, a->ldb, a->b_batch_stride,
+                       pair ? BN / 2 : BN);
   else
     rc = make_bf16_map(&mb, a->B, a->N, a->K, a->batch, a->ldb, a->b_batch_stride, BK);
   if (rc) return rc;
@@ -706,25 +829,38 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   p.pre_is_grad = a->pre_is_grad;
   p.mt_offset = a->mt_offset > 0 ? static_cast<int>(a->mt_offset % ((a->M + BM - 1) / BM)) : 0;
 
-  static int sm_count = 0;
-  static bool attr_set = false;
-  if (!attr_set) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) {
-      set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
-      return -4;
+  if (pair) {
+    const long long num_m2 = (a->M + 2 * BM - 1) / (2 * BM), num_n = (a->N + BN - 1) / BN;
+    const long long tiles = a->batch * num_m2 * num_n * p.split_k;
+    int limit = max_pairs;
+    if (a->num_sms > 0 && a->num_sms / 2 < limit) limit = a->num_sms / 2 > 0 ? a->num_sms / 2 : 1;
+    const int pairs = static_cast<int>(tiles < limit ? tiles : limit);
+    p.mt_offset = a->mt_offset > 0 ? static_cast<int>(a->mt_offset % (2 * num_m2)) : 0;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<true>, ma, mb, mc, mc2, p);
+    if (le != cudaSuccess) {
+      set_error("%s (code %d)", cudaGetErrorString(le), static_cast<int>(le));
+      return -5;
     }
-    attr_set = true;
+    return 0;
   }
   const long long num_m = (a->M + BM - 1) / BM, num_n = (a->N + BN - 1) / BN;
   const long long tiles = a->batch * num_m * num_n * p.split_k;
   int max_ctas = a->num_sms > 0 ? a->num_sms : sm_count;
   int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
-  gemm_bf16_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, p);
+  gemm_bf16_kernel<false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));

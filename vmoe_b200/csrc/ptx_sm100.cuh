@@ -197,6 +197,80 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, int a_mn_ma
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// ----------------------------------------------------------------------------- CTA pairs
+// Helpers for kernels launched as clusters of two CTAs that drive one tcgen05.mma together
+// (cta_group::2): the even CTA of the pair issues the MMAs, each CTA stages its own rows of A
+// and its half of B, and each CTA's TMEM receives the accumulator rows of its own A tile.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of `smem_addr` (a shared::cta address of this CTA) inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier given by a shared::cluster address (possibly in the peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// 3-D tiled load into this CTA's shared memory whose completion bytes are counted on an
+// mbarrier given by a shared::cluster address (the leader CTA's barrier). Not a multicast:
+// the data lands only in the executing CTA.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* desc,
+                                                 uint32_t bar_cluster_addr, int c0, int c1,
+                                                 int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+        "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the CTA pair (M = 256: 128 rows per CTA).
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Once all earlier MMAs of this thread complete, arrive on the mbarrier at this shared-memory
+// offset in every CTA of `cta_mask` (an arrival signal only; no data is multicast).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
+}
+
 // ----------------------------------------------------------------------------- math helpers
 __device__ __forceinline__ float tanh_approx(float x) {
   float y;
@@ -216,6 +290,66 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float t = tanh_approx(u);
   float du = k0 * (1.0f + 3.0f * k1 * x2);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
+// ---- packed fp32 pairs (Blackwell executes add/mul/fma on two fp32 values per instruction)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// GELU (tanh form) and its derivative for two values, sharing one tanh per value:
+// 12 packed instructions + 2 tanh for the pair.
+__device__ __forceinline__ void gelu_and_grad_pair(float x0, float x1, float& g0, float& g1,
+                                                   float& d0, float& d1) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const f32x2 x = f2_pack(x0, x1);
+  const f32x2 x2 = f2_mul(x, x);
+  const f32x2 w = f2_fma(x2, f2_pack(k0 * k1, k0 * k1), f2_pack(k0, k0));  // k0 (1 + k1 x^2)
+  float u0, u1;
+  f2_unpack(f2_mul(x, w), u0, u1);
+  const float t0 = tanh_approx(u0), t1 = tanh_approx(u1);
+  const f32x2 t = f2_pack(t0, t1);
+  const f32x2 hp = f2_fma(t, f2_pack(0.5f, 0.5f), f2_pack(0.5f, 0.5f));       // 0.5 (1 + t)
+  const f32x2 omt2 = f2_fma(f2_mul(t, t), f2_pack(-1.f, -1.f), f2_pack(1.f, 1.f));
+  const f32x2 du = f2_fma(x2, f2_pack(3.f * k0 * k1, 3.f * k0 * k1), f2_pack(k0, k0));
+  const f32x2 hx = f2_mul(x, f2_pack(0.5f, 0.5f));
+  f2_unpack(f2_mul(x, hp), g0, g1);
+  f2_unpack(f2_fma(f2_mul(hx, omt2), du, hp), d0, d1);
+}
+__device__ __forceinline__ void gelu_pair(float x0, float x1, float& g0, float& g1) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const f32x2 x = f2_pack(x0, x1);
+  const f32x2 x2 = f2_mul(x, x);
+  const f32x2 w = f2_fma(x2, f2_pack(k0 * k1, k0 * k1), f2_pack(k0, k0));
+  float u0, u1;
+  f2_unpack(f2_mul(x, w), u0, u1);
+  const f32x2 t = f2_pack(tanh_approx(u0), tanh_approx(u1));
+  const f32x2 hx = f2_mul(x, f2_pack(0.5f, 0.5f));
+  f2_unpack(f2_fma(hx, t, hx), g0, g1);  // 0.5 x (1 + t)
+}
+__device__ __forceinline__ void gelu_grad_pair(float x0, float x1, float& d0, float& d1) {
+  float g0, g1;
+  gelu_and_grad_pair(x0, x1, g0, g1, d0, d1);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

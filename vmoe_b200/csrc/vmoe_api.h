@@ -53,6 +53,7 @@ typedef struct VmoeGemmArgs {
   int32_t c2_gelu_grad;  // with act == 1: C2 receives gelu'(v) instead of v
   int32_t pre_is_grad;   // gelu_pre already holds gelu'(x): multiply by it as is
   int32_t mt_offset;     // m-tiles are visited starting from this tile (rotation)
+  int32_t cta_pair;      // 0: choose by size, 1: one CTA per 128x256 tile, 2: CTA pairs (256x256)
 } VmoeGemmArgs;
 
 VMOE_API int vmoe_gemm_bf16(const VmoeGemmArgs* args, vmoe_stream_t stream);

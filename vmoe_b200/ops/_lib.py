@@ -55,6 +55,7 @@ class GemmArgs(ctypes.Structure):
       ("a_ready_epoch", ctypes.c_uint32), ("num_sms", ctypes.c_int32),
       ("c2_gelu_grad", ctypes.c_int32), ("pre_is_grad", ctypes.c_int32),
       ("mt_offset", ctypes.c_int32),
+      ("cta_pair", ctypes.c_int32),
   ]
 
 

@@ -76,7 +76,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
          accumulate: bool = False, split_k: int = 1, a_ready: Optional[torch.Tensor] = None,
          a_ready_epoch: int = 0, status: Optional[torch.Tensor] = None,
          num_sms: int = 0, out_pre_is_grad: bool = False,
-         gelu_pre_is_grad: bool = False, mt_offset: int = 0) -> torch.Tensor:
+         gelu_pre_is_grad: bool = False, mt_offset: int = 0,
+         cta_pair: int = 0) -> torch.Tensor:
   """``out = epilogue(a @ b^T)``; see ``csrc/vmoe_api.h`` for the epilogue order."""
   if not a.is_cuda:
     return gemm_reference(a, b, a_mn_major=a_mn_major, b_mn_major=b_mn_major, bias=bias,
@@ -152,6 +153,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
   args.c2_gelu_grad = int(out_pre_is_grad)
   args.pre_is_grad = int(gelu_pre_is_grad)
   args.mt_offset = int(mt_offset)
+  args.cta_pair = int(cta_pair)
   rc = _lib.lib().vmoe_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
   _lib.check(rc, "vmoe_gemm_bf16")
   _lib.count_launch()
