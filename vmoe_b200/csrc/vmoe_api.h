@@ -82,6 +82,19 @@ VMOE_API int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamm
 //    in it has to be zero on entry, because every launch overwrites the rows it later reads.
 //  * Calls that overlap in time on one device (different streams or threads) race on the array;
 //    serialise them.
+// All-reduce (sum) of the fp32 range [offset, offset + count) of a symmetric gradient buffer
+// over `world` ranks with peer loads (two kernels: reduce own slice, gather the others).
+// bufs / flags: host arrays of `world` device addresses (gradient buffer base and counter base
+// of every rank; counters are uint32 [3][num_ranges], zero-initialised once). `epoch` counts
+// calls for this range starting at 1. local_counters: uint32 [2][num_ranges] private to the
+// rank, zero-initialised. Before the range is written again the caller must wait until
+// counters[2 * num_ranges + range] >= epoch * world (vmoe_wait_counters).
+VMOE_API int vmoe_allreduce_range(const uint64_t* bufs, const uint64_t* flags, int32_t world,
+                                  int32_t rank, int64_t offset, int64_t count, int32_t range,
+                                  int32_t num_ranges, uint32_t epoch, uint32_t* local_counters,
+                                  uint32_t* status, int32_t ctas, int64_t limit_cycles,
+                                  vmoe_stream_t stream);
+
 //  * Returns -1 with a message in vmoe_last_error() when h > 1024.
 VMOE_API int vmoe_layernorm_bwd_static(const void* dy, const void* x, const float* gamma,
                                        const float* mean, const float* rstd, const void* dres,

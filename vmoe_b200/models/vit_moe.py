@@ -22,6 +22,7 @@ from torch import nn
 from vmoe_b200 import moe
 from vmoe_b200 import ops
 from vmoe_b200.models import routing
+from vmoe_b200.parallel import grad_allreduce
 from vmoe_b200.parallel import mesh as mesh_lib
 from vmoe_b200.parallel.exchange import ExpertExchange
 from vmoe_b200.utils.misc import parse_call
@@ -394,11 +395,15 @@ class EncoderMoe(nn.Module):
     metrics: Dict[str, Any] = {}
     last_block = self.num_layers if last_block is None else last_block
     for block in range(first_block, last_block):
+      # In backward, the gradient of this tensor means blocks >= `block` have their parameter
+      # gradients: the data-parallel reducer starts all-reducing them right away.
+      x = grad_allreduce.grad_marker(x, block)
       out = getattr(self, f"encoderblock_{block}")(x)
       if isinstance(out, tuple):
         x, metrics[f"encoderblock_{block}"] = out
       else:
         x = out
+    x = grad_allreduce.grad_marker(x, last_block)
     encoded = self.encoder_norm(x) if final_norm else x
     aux = [m["auxiliary_loss"] for m in metrics.values()]
     metrics["auxiliary_loss"] = sum(aux) if aux else torch.zeros((), device=x.device)

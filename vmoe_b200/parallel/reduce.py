@@ -15,9 +15,13 @@ import torch.distributed as dist
 def reduce_gradients(optimizer, mesh) -> None:
   if mesh is None or mesh.world_size == 1 or not dist.is_initialized():
     return
+  reducer = getattr(optimizer, "grad_reducer", None)
   for kind, bucket in optimizer.buckets.items():
     bucket.rebind_grads()
     if kind == "dense":
-      dist.all_reduce(bucket.grads, group=mesh.world_group)
+      if reducer is not None and reducer._armed:
+        reducer.finish()  # ranges were reduced during backward by the peer-memory kernels
+      else:
+        dist.all_reduce(bucket.grads, group=mesh.world_group)
     elif mesh.num_replicas > 1:
       dist.all_reduce(bucket.grads, group=mesh.replica_group)

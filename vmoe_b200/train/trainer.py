@@ -116,6 +116,9 @@ def train_step(state: TrainState, images: Tensor, labels: Tensor,
     im = images if n == 1 else images[i::n]
     lb = labels if n == 1 else labels[i::n]
     total, m = compute_loss_and_metrics(state, im, lb, loss_fn)
+    reducer = getattr(state.optimizer, "grad_reducer", None)
+    if reducer is not None and i == n - 1:
+      reducer.begin()  # gradients are complete after this backward: reduce them as they appear
     total.backward()
     m = {k: (v.detach() if isinstance(v, torch.Tensor) else v) for k, v in m.items()}
     metrics = m if metrics is None else _tree_add(metrics, _detach_tree(m))
@@ -157,6 +160,8 @@ def create_train_state(*, model_config: Mapping[str, Any], optimizer_config: Map
                     else optimizer_config)
   named = [(key, p) for key, _, p in naming.named_flax_parameters(model, prefix="params")]
   opt = optimizer_lib.create_optimizer(named, total_steps=total_steps, mesh=mesh, **opt_kwargs)
+  from vmoe_b200.parallel import grad_allreduce
+  opt.grad_reducer = grad_allreduce.maybe_create(opt, mesh, model)
   rngs = misc.make_rngs(tuple(extra_rng_keys) + ("dropout", "gating"), seed)
   return TrainState(model=model, optimizer=opt, step=0, rngs=rngs, mesh=mesh)
 
