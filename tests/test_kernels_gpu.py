@@ -227,3 +227,22 @@ def test_gating_logits_gemm():
   _close(out, out2, 1e-3)
   _close(x.grad, x2.grad, 1e-2)
   _close(w.grad, w2.grad, 1e-2)
+
+
+def test_layer_norm_fork_adds_residual_gradient():
+  torch.manual_seed(0)
+  h = 768
+  x = (torch.randn(777, h, device=DEV) * 2).bfloat16().requires_grad_()
+  w = torch.randn(h, device=DEV).requires_grad_()
+  b = torch.randn(h, device=DEV).requires_grad_()
+  y, xr = ops.layer_norm_fork(x, w, b, 1e-6)
+  dy, dr = torch.randn_like(y), torch.randn_like(y)
+  torch.autograd.backward([y, xr], [dy, dr])
+  x2 = x.detach().float().requires_grad_()
+  w2, b2 = w.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+  y2 = F.layer_norm(x2, (h,), w2, b2, 1e-6)
+  torch.autograd.backward([y2, x2 * 1.0], [dy.float(), dr.float()])
+  _close(y, y2, 2e-2)
+  _close(x.grad, x2.grad, 2e-2)
+  _close(w.grad, w2.grad, 1e-2)
+  _close(b.grad, b2.grad, 1e-2)

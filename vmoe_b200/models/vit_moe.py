@@ -61,6 +61,10 @@ class LayerNorm(nn.Module):
   def forward(self, x: Tensor) -> Tensor:
     return ops.layer_norm(x, self.scale, self.bias, self.eps)
 
+  def fork(self, x: Tensor):
+    """``(self(x), x)`` with the residual branch's gradient fused into the backward kernel."""
+    return ops.layer_norm_fork(x, self.scale, self.bias, self.eps)
+
 
 class Dense(nn.Module):
   """``y = x W^T + b`` with ``weight: [out, in]`` (fp32 master, bf16 tensor-core compute)."""
@@ -291,12 +295,12 @@ class EncoderBlock(nn.Module):
       self.Mlp = mlp
 
   def forward(self, inputs: Tensor):
-    x = self.LayerNorm_0(inputs)
+    x, inputs = self.LayerNorm_0.fork(inputs)
     if self.training and self.dropout_rate > 0:
       x = F.dropout(self.SelfAttention(x), self.dropout_rate, True) + inputs
     else:
       x = self.SelfAttention(x, residual=inputs)  # residual add fused in the GEMM epilogue
-    y = self.LayerNorm_1(x)
+    y, x = self.LayerNorm_1.fork(x)
     if self.is_moe:
       return self.Moe(y, residual=x)
     return self.Mlp(y, residual=x)

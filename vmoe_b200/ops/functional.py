@@ -232,6 +232,17 @@ def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
   return F.layer_norm(x, (x.shape[-1],), w, b, eps)
 
 
+def layer_norm_fork(x: torch.Tensor, weight: Optional[torch.Tensor],
+                    bias: Optional[torch.Tensor], eps: float = 1e-6):
+  """``(layer_norm(x), x)``. On the CUDA path the second value is routed through the same
+  autograd node, so the gradient of the residual branch is added inside the LayerNorm
+  backward kernel."""
+  if _fast(x) and x.shape[-1] % 8 == 0 and x.requires_grad and torch.is_grad_enabled():
+    from vmoe_b200.ops import norm
+    return norm.layer_norm_fork(x, weight, bias, eps)
+  return layer_norm(x, weight, bias, eps), x
+
+
 # ----------------------------------------------------------------------------------- attention
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               dropout_p: float = 0.0, training: bool = False) -> torch.Tensor:

@@ -31,33 +31,80 @@ class _LayerNormFn(torch.autograd.Function):
     _lib.count_launch()
     ctx.save_for_backward(x2, weight, mean, rstd)
     ctx.has_bias = bias is not None
+    ctx.bias_ref = bias
     ctx.shape = x.shape
     return y.reshape(x.shape)
 
   @staticmethod
   def backward(ctx, dy):
-    x2, weight, mean, rstd = ctx.saved_tensors
-    rows, h = x2.shape
-    dy2 = dy.reshape(rows, h)
-    if not dy2.is_contiguous():
-      dy2 = dy2.contiguous()
-    dx = torch.empty_like(x2)
-    dgamma = torch.zeros(h, dtype=torch.float32, device=dy.device) if weight is not None else None
-    dbeta = torch.zeros(h, dtype=torch.float32, device=dy.device) if ctx.has_bias else None
-    lib = _lib.lib()
-    lib.vmoe_layernorm_bwd_scratch_bytes.restype = ctypes.c_int64
-    nbytes = lib.vmoe_layernorm_bwd_scratch_bytes(ctypes.c_int64(rows), ctypes.c_int64(h))
-    scratch = torch.empty(max(int(nbytes) // 4, 1), dtype=torch.float32, device=dy.device)
-    rc = lib.vmoe_layernorm_bwd(
-        _vp(dy2.data_ptr()), _vp(x2.data_ptr()), _vp(_lib.ptr(weight)), _vp(mean.data_ptr()),
-        _vp(rstd.data_ptr()), _vp(None), _vp(dx.data_ptr()), _vp(_lib.ptr(dgamma)),
-        _vp(_lib.ptr(dbeta)), _vp(scratch.data_ptr()), ctypes.c_int64(rows), ctypes.c_int64(h),
-        _vp(_lib.stream_ptr()))
-    _lib.check(rc, "vmoe_layernorm_bwd")
-    _lib.count_launch(2)
-    return dx.reshape(ctx.shape), dgamma, dbeta, None
+    return _backward(ctx, dy, None) + (None,)
+
+
+def _grad_or_new(p, h, device):
+  """``(buffer the kernel accumulates into, value to hand to autograd)`` for dgamma / dbeta:
+  the parameter's bound fp32 gradient when there is one (nothing returned to autograd), else
+  a fresh zero tensor."""
+  from vmoe_b200.ops.functional import _grad_target
+  if p is None:
+    return None, None
+  tgt = _grad_target(p)
+  if tgt is not None:
+    return tgt, None
+  new = torch.zeros(h, dtype=torch.float32, device=device)
+  return new, new
+
+
+def _backward(ctx, dy, dres):
+  x2, weight, mean, rstd = ctx.saved_tensors
+  rows, h = x2.shape
+  if dy is None:
+    dy = torch.zeros_like(x2)
+  dy2 = dy.reshape(rows, h)
+  if not dy2.is_contiguous():
+    dy2 = dy2.contiguous()
+  if dres is not None:
+    dres = dres.reshape(rows, h)
+    if not dres.is_contiguous() or dres.dtype != torch.bfloat16:
+      dres = dres.contiguous().to(torch.bfloat16)
+  dx = torch.empty_like(x2)
+  dgamma_buf, dgamma = _grad_or_new(weight, h, dy.device)
+  dbeta_buf, dbeta = _grad_or_new(ctx.bias_ref if ctx.has_bias else None, h, dy.device)
+  lib = _lib.lib()
+  lib.vmoe_layernorm_bwd_scratch_bytes.restype = ctypes.c_int64
+  nbytes = lib.vmoe_layernorm_bwd_scratch_bytes(ctypes.c_int64(rows), ctypes.c_int64(h))
+  scratch = torch.empty(max(int(nbytes) // 4, 1), dtype=torch.float32, device=dy.device)
+  rc = lib.vmoe_layernorm_bwd(
+      _vp(dy2.data_ptr()), _vp(x2.data_ptr()), _vp(_lib.ptr(weight)), _vp(mean.data_ptr()),
+      _vp(rstd.data_ptr()), _vp(_lib.ptr(dres)), _vp(dx.data_ptr()), _vp(_lib.ptr(dgamma_buf)),
+      _vp(_lib.ptr(dbeta_buf)), _vp(scratch.data_ptr()), ctypes.c_int64(rows), ctypes.c_int64(h),
+      _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_layernorm_bwd")
+  _lib.count_launch(2)
+  return dx.reshape(ctx.shape), dgamma, dbeta
+
+
+class _LayerNormForkFn(_LayerNormFn):
+  """``(LayerNorm(x), x)``: the second output is ``x`` itself, for the residual branch. Because
+  both consumers hang off this one node, backward receives both gradients at once and the
+  kernel adds the residual gradient while it writes dx, instead of autograd running a separate
+  full-size add."""
+
+  @staticmethod
+  def forward(ctx, x, weight, bias, eps):
+    y = _LayerNormFn.forward(ctx, x, weight, bias, eps)
+    return y, x.view_as(x)
+
+  @staticmethod
+  def backward(ctx, dy, dres):
+    return _backward(ctx, dy, dres) + (None,)
 
 
 def layer_norm(x, weight, bias, eps=1e-6):
   assert weight is None or weight.dtype == torch.float32
   return _LayerNormFn.apply(x, weight, bias, eps)
+
+
+def layer_norm_fork(x, weight, bias, eps=1e-6):
+  """Returns ``(LayerNorm(x), x)``; use the second value for the residual connection."""
+  assert weight is None or weight.dtype == torch.float32
+  return _LayerNormForkFn.apply(x, weight, bias, eps)
