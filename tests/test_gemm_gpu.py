@@ -98,3 +98,17 @@ def test_gemm_pair_large_matches_single():
   assert status.item() == 0
   assert torch.equal(one, two)
   _check(two, G.gemm_reference(a, b, bias=bias, out_dtype=torch.float32))
+
+
+@pytest.mark.parametrize("pair", [1, 2])
+def test_gemm_multi_destination_output(pair):
+  """Row blocks of the output go to separate tensors (stand-ins for peer buffers)."""
+  torch.manual_seed(4)
+  e, rows, dests, n, k = 2, 96, 3, 200, 128
+  a, b = _rand(e, rows * dests, k), _rand(e, n, k)
+  bias = torch.randn(e, n, device=DEV)
+  outs = [torch.zeros(e, rows, n, device=DEV, dtype=torch.bfloat16) for _ in range(dests)]
+  G.gemm(a, b, bias=bias, out_multi=outs, cta_pair=pair)
+  ref = G.gemm_reference(a, b, bias=bias, out_dtype=torch.float32)
+  for j, o in enumerate(outs):
+    _check(o, ref[:, j * rows:(j + 1) * rows])

@@ -70,6 +70,13 @@ struct GemmParams {
   int c2_gelu_grad;  // C2 receives gelu'(pre-activation) instead of the pre-activation
   int pre_is_grad;   // gelu_pre already holds gelu'(x): plain multiply
   int mt_offset;     // rotation of the m-tile order
+  int c_multi_rows;  // > 0: rows per destination block of the multi-destination output
+};
+
+// Output split over several destinations (row block j of every batch goes to destination j).
+constexpr int MAX_C_DESTS = 8;
+struct CMultiMaps {
+  CUtensorMap m[MAX_C_DESTS];
 };
 
 struct TileCoord {
@@ -115,7 +122,7 @@ template <bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_c2,
-                 const GemmParams p) {
+                 const __grid_constant__ CMultiMaps cmaps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -590,7 +597,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           fence_proxy_async();  // make the staged tile visible to the TMA engine
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tma_c, smem_u32(stage_c), col0, row0, t.b);
+            if (p.c_multi_rows > 0) {
+              // Row block j of the output lives in destination j (possibly a peer GPU's buffer).
+              // Boxes that start past the last row have no destination (and no map): skip them.
+              if (row0 < p.M) {
+                const int j = row0 / p.c_multi_rows;
+                tma_store_3d(&cmaps.m[j], smem_u32(stage_c), col0, row0 - j * p.c_multi_rows,
+                             t.b);
+              }
+            } else {
+              tma_store_3d(&tma_c, smem_u32(stage_c), col0, row0, t.b);
+            }
             if (p.C2) tma_store_3d(&tma_c2, smem_u32(stage_c2), col0, row0, t.b);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
@@ -797,8 +814,32 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
       if (rc) return rc;
     }
   }
+  static CMultiMaps cm_zero;  // zero-initialised; copied when the output has one destination
+  CMultiMaps cm = cm_zero;
+  int c_multi_rows = 0;
+  if (a->c_multi_count > 0) {
+    if (!tma_store || a->C2 != nullptr || a->c_multi_count > MAX_C_DESTS ||
+        a->c_multi_rows <= 0 || a->c_multi_rows % 32 ||
+        a->c_multi_rows * a->c_multi_count < a->M) {
+      set_error("%s (code %d)",
+                "multi-destination output needs bf16 TMA stores, no second output, <= 8 "
+                "destinations and a row block that is a multiple of 32", 0);
+      return -1;
+    }
+    for (int j = 0; j < a->c_multi_count; ++j) {
+      if (reinterpret_cast<uintptr_t>(a->c_multi[j]) & 15) {
+        set_error("%s (code %d)", "multi-destination output bases must be 16-byte aligned", j);
+        return -1;
+      }
+      rc = make_bf16_map(&cm.m[j], a->c_multi[j], a->N, a->c_multi_rows, a->batch, a->ldc,
+                         a->c_batch_stride, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+    }
+    c_multi_rows = static_cast<int>(a->c_multi_rows);
+  }
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.c_multi_rows = c_multi_rows;
   p.tma_store = tma_store ? 1 : 0;
   p.C = a->C;
   p.C2 = a->C2;
@@ -849,7 +890,7 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     cfg.stream = stream;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<true>, ma, mb, mc, mc2, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<true>, ma, mb, mc, mc2, cm, p);
     if (le != cudaSuccess) {
       set_error("%s (code %d)", cudaGetErrorString(le), static_cast<int>(le));
       return -5;
@@ -860,7 +901,7 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   const long long tiles = a->batch * num_m * num_n * p.split_k;
   int max_ctas = a->num_sms > 0 ? a->num_sms : sm_count;
   int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
-  gemm_bf16_kernel<false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, p);
+  gemm_bf16_kernel<false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, cm, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));

@@ -54,6 +54,12 @@ typedef struct VmoeGemmArgs {
   int32_t pre_is_grad;   // gelu_pre already holds gelu'(x): multiply by it as is
   int32_t mt_offset;     // m-tiles are visited starting from this tile (rotation)
   int32_t cta_pair;      // 0: choose by size, 1: one CTA per 128x256 tile, 2: CTA pairs (256x256)
+  // Multi-destination bf16 output: when c_multi_count > 0, rows [j * c_multi_rows,
+  // (j + 1) * c_multi_rows) of every batch are stored to c_multi[j] (same ldc / batch stride as
+  // C, which is then only used for alignment checks). Destinations may be peer-GPU buffers.
+  const void* c_multi[8];
+  int32_t c_multi_count;
+  int64_t c_multi_rows;
 } VmoeGemmArgs;
 
 VMOE_API int vmoe_gemm_bf16(const VmoeGemmArgs* args, vmoe_stream_t stream);

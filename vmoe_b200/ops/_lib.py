@@ -56,6 +56,9 @@ class GemmArgs(ctypes.Structure):
       ("c2_gelu_grad", ctypes.c_int32), ("pre_is_grad", ctypes.c_int32),
       ("mt_offset", ctypes.c_int32),
       ("cta_pair", ctypes.c_int32),
+      ("c_multi", ctypes.c_void_p * 8),
+      ("c_multi_count", ctypes.c_int32),
+      ("c_multi_rows", ctypes.c_int64),
   ]
 
 

@@ -77,7 +77,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
          a_ready_epoch: int = 0, status: Optional[torch.Tensor] = None,
          num_sms: int = 0, out_pre_is_grad: bool = False,
          gelu_pre_is_grad: bool = False, mt_offset: int = 0,
-         cta_pair: int = 0) -> torch.Tensor:
+         cta_pair: int = 0, out_multi=None) -> torch.Tensor:
   """``out = epilogue(a @ b^T)``; see ``csrc/vmoe_api.h`` for the epilogue order."""
   if not a.is_cuda:
     return gemm_reference(a, b, a_mn_major=a_mn_major, b_mn_major=b_mn_major, bias=bias,
@@ -99,12 +99,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
   else:
     N, Kb = b3.shape[1], b3.shape[2]
   assert K == Kb, (a.shape, b.shape, a_mn_major, b_mn_major)
-  if out is None:
+  if out_multi:
+    out = out_multi[0]  # layout and dtype of every destination
+  elif out is None:
     shape = (M, N) if a.dim() == 2 else (batch, M, N)
     out = torch.empty(shape, dtype=out_dtype, device=a.device)
     assert not accumulate
   o3 = _as3d(out)
-  assert o3.stride(-1) == 1 and o3.shape[-2:] == (M, N), (o3.shape, M, N)
+  assert o3.stride(-1) == 1 and (out_multi or o3.shape[-2:] == (M, N)), (o3.shape, M, N)
   args = _lib.GemmArgs()
   args.A, args.B, args.C = a3.data_ptr(), b3.data_ptr(), o3.data_ptr()
   args.M, args.N, args.K, args.batch = M, N, K, batch
@@ -154,6 +156,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
   args.pre_is_grad = int(gelu_pre_is_grad)
   args.mt_offset = int(mt_offset)
   args.cta_pair = int(cta_pair)
+  if out_multi:
+    # Row block j of every batch goes to out_multi[j] (all of shape (batch, rows, N), same
+    # strides as ``out``, which only provides the layout and is not written).
+    d0 = _as3d(out_multi[0])
+    assert len(out_multi) <= 8 and d0.dtype == torch.bfloat16
+    assert d0.shape[0] == batch and d0.shape[2] == N and d0.shape[1] * len(out_multi) >= M
+    for j, d in enumerate(out_multi):
+      dj = _as3d(d)
+      assert dj.shape == d0.shape and dj.stride() == d0.stride()
+      args.c_multi[j] = dj.data_ptr()
+    args.c_multi_count = len(out_multi)
+    args.c_multi_rows = d0.shape[1]
+    args.ldc = d0.stride(1)
+    args.c_batch_stride = d0.stride(0) if batch > 1 else 0
   rc = _lib.lib().vmoe_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
   _lib.check(rc, "vmoe_gemm_bf16")
   _lib.count_launch()

@@ -258,10 +258,17 @@ class _P2PMoeFn(torch.autograd.Function):
     hid = gemm(comm.xe, w1h, bias=b1, act=ACT_GELU, out_pre=pre, out_pre_is_grad=True,
                a_ready=comm.fx, a_ready_epoch=comm.epoch["x"], status=comm.status,
                mt_offset=comm.mt_offset)
-    for i in range(ep):
-      src = (rank + i) % ep
-      gemm(hid[:, src * r:(src + 1) * r], w2h, bias=b2, out=comm.home_out("YB", src))
-      signal(comm.done_flag_addr("FY", src))
+    if r % 32 == 0 and ep <= 8:
+      # One GEMM over all rows; every 32-row output box is TMA-stored straight into the home
+      # buffer of the rank its rows came from.
+      gemm(hid, w2h, bias=b2, out_multi=[comm.home_out("YB", src) for src in range(ep)])
+      for src in range(ep):
+        signal(comm.done_flag_addr("FY", src))
+    else:
+      for i in range(ep):
+        src = (rank + i) % ep
+        gemm(hid[:, src * r:(src + 1) * r], w2h, bias=b2, out=comm.home_out("YB", src))
+        signal(comm.done_flag_addr("FY", src))
     wait_counters(comm.fy, ep, comm.epoch["y"], comm.status)
     out = torch.empty_like(x)
     combine_rows(comm.yb_table, expert, slot, gate, residual, out, g, s, e, c, k, h)
@@ -298,10 +305,17 @@ class _P2PMoeFn(torch.autograd.Function):
     db2 = bias_grad(comm.dye, b2)
     dw2 = wgrad(comm.dye, hid, w2)
     dw1 = wgrad(dpre, comm.xe, w1)
-    for i in range(ep):
-      src = (rank + i) % ep
-      gemm(dpre[:, src * r:(src + 1) * r], w1h, b_mn_major=True, out=comm.home_out("DXB", src))
-      signal(comm.done_flag_addr("FDX", src))
+    if r % 32 == 0 and ep <= 8:
+      gemm(dpre, w1h, b_mn_major=True,
+           out_multi=[comm.home_out("DXB", src) for src in range(ep)])
+      for src in range(ep):
+        signal(comm.done_flag_addr("FDX", src))
+    else:
+      for i in range(ep):
+        src = (rank + i) % ep
+        gemm(dpre[:, src * r:(src + 1) * r], w1h, b_mn_major=True,
+             out=comm.home_out("DXB", src))
+        signal(comm.done_flag_addr("FDX", src))
     wait_counters(comm.fdx, ep, comm.epoch["dx"], comm.status)
     dx = torch.empty(g, s, h, dtype=torch.bfloat16, device=dev)
     combine_rows(comm.dxb_table, expert, slot, None, None, dx, g, s, e, c, k, h)
