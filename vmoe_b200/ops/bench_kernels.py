@@ -72,18 +72,15 @@ def layernorm(rows: int, iters: int):
 def attention(rows: int, iters: int):
   from vmoe_b200 import ops
   batch = max(rows // 197, 1)
-  qkv = torch.randn(batch, 197, 3 * 768, device="cuda").bfloat16().requires_grad_()
-  out = ops.attention_packed(qkv, 12)
+  qkv = torch.randn(batch, 197, 3, 12, 64, device="cuda").bfloat16().requires_grad_()
+  out = ops.attention_packed(qkv)
   g = torch.randn_like(out)
-  us_f = _timed(lambda: ops.attention_packed(qkv, 12), iters)
+  us_f = _timed(lambda: ops.attention_packed(qkv), iters)
 
-  def both():
-    ops.attention_packed(qkv, 12).backward(g)
-
-  us_fb = _timed(both, iters)
+  us_b = _timed(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), iters)
   flops = 4 * batch * 12 * 197 * 197 * 64
   print(f"attention fwd: {us_f:.1f} us ({flops / us_f / 1e6:.0f} TFLOP/s useful); "
-        f"fwd+bwd: {us_fb:.1f} us")
+        f"bwd: {us_b:.1f} us ({2.5 * flops / us_b / 1e6:.0f} TFLOP/s useful)")
 
 
 def router(rows: int, iters: int):
