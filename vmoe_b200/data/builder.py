@@ -101,6 +101,8 @@ class SyntheticBuilder(DatasetBuilder):
   shuffle_files: bool = False
   shuffle_seed: Optional[int] = None
   seed: int = 0
+  text_len: int = 0       # > 0: every example also has "text", that many token ids
+  vocab_size: int = 32_000
 
   def _split_size(self) -> int:
     return self.num_train_examples if self.split.startswith("train") else self.num_eval_examples
@@ -118,7 +120,10 @@ class SyntheticBuilder(DatasetBuilder):
       labels = rng.integers(0, self.num_classes, (k,), dtype=np.int64)
     else:
       labels = np.int64(rng.integers(0, self.num_classes))
-    return {"image": image, "label": labels, "labels": labels}
+    out = {"image": image, "label": labels, "labels": labels}
+    if self.text_len > 0:
+      out["text"] = rng.integers(2, self.vocab_size, (self.text_len,), dtype=np.int64).astype(np.int32)
+    return out
 
   def as_dataset(self) -> Iterator[Dict[str, Any]]:
     idx, cnt = _process_index_count()
