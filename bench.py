@@ -155,9 +155,24 @@ def main() -> int:
   mesh = mesh_lib.get_auto_logical_mesh(num_partitions)
   mesh_lib.set_mesh(mesh)
 
-  cfg = common.get_vmoe_config(args.model, IMAGE_SIZE, NUM_CLASSES)
-  cfg.encoder.dtype = "bfloat16"
-  cfg.encoder.moe.router.dispatcher.batch_priority = True
+  if args.model.startswith("soft-"):
+    # Secondary workload: Soft MoE (e.g. "soft-b16": 128 experts x 1 slot in the last 6 blocks).
+    from vmoe_b200.projects.soft_moe.configs import common as soft_common
+    from vmoe_b200.projects.soft_moe.configs import pretrain_jft4b
+    variant, patch = args.model[5].upper(), int(args.model[6:])
+    e, last_n = pretrain_jft4b.get_default_moe_num_experts_and_last_n(variant, patch)
+    cfg = soft_common.get_vmoe_soft_router_config(
+        variant, patch, NUM_CLASSES, image_size=IMAGE_SIZE, num_experts=e, last_n=last_n,
+        capacity_factor=None, num_slots=1)
+    cfg.encoder.moe.router.compute_similarity_metrics = False
+    cfg.encoder.dtype = "bfloat16"
+    num_partitions = min(e, world)
+    mesh = mesh_lib.get_auto_logical_mesh(num_partitions)
+    mesh_lib.set_mesh(mesh)
+  else:
+    cfg = common.get_vmoe_config(args.model, IMAGE_SIZE, NUM_CLASSES)
+    cfg.encoder.dtype = "bfloat16"
+    cfg.encoder.moe.router.dispatcher.batch_priority = True
   opt_cfg = dict(name="adam", b1=0.9, b2=0.999, weight_decay=0.1,
                  learning_rate=dict(schedule="warmup_linear_decay", peak_value=8e-4,
                                     end_value=1e-5, warmup_steps=10_000))
@@ -242,7 +257,8 @@ def main() -> int:
   if rank == 0:
     value = batch * world / (ms_per_step / 1e3)
     out = {
-        "metric": "V-MoE B/16 train images/s",
+        "metric": ("V-MoE B/16 train images/s" if args.model == MODEL_DESC
+                   else f"{args.model} train images/s"),
         "value": value,
         "unit": "images/s",
         "n_gpus": world,
@@ -256,7 +272,8 @@ def main() -> int:
         "data": "synthetic images uniform[-1,1] 224x224x3, 21843-way multi-hot labels; random-init weights",
         "impl": "library-ops stand-in" if args.library_ops else "vmoe_b200",
         "config": {
-            "model": "V-MoE B/16, 8 experts every odd block, K=2, capacity 1.05, BPR, sigmoid xent, Adam wd 0.1",
+            "model": ("V-MoE B/16, 8 experts every odd block, K=2, capacity 1.05, BPR, sigmoid xent, Adam wd 0.1"
+                      if args.model == MODEL_DESC else args.model),
             "global_batch": batch * world,
             "seq_len": 197,
             "parallelism": f"dp{world} x ep{num_partitions}",

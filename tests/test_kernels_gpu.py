@@ -246,3 +246,28 @@ def test_layer_norm_fork_adds_residual_gradient():
   _close(x.grad, x2.grad, 2e-2)
   _close(w.grad, w2.grad, 1e-2)
   _close(b.grad, b2.grad, 1e-2)
+
+
+@pytest.mark.parametrize("g,s,n,h", [(5, 196, 128, 768), (3, 50, 16, 64), (2, 197, 264, 128)])
+def test_einsum_dispatch_combine_on_gemm(g, s, n, h):
+  from vmoe_b200.ops import einsum_ops
+  torch.manual_seed(0)
+  logits = torch.randn(g, s, n, device=DEV)
+  wd = torch.softmax(logits, dim=1).requires_grad_()
+  wc = torch.softmax(logits, dim=2).requires_grad_()
+  x = torch.randn(g, s, h, device=DEV).bfloat16().requires_grad_()
+  assert einsum_ops.supported(wd, x)
+  xe = einsum_ops.dispatch(wd, x)
+  out = einsum_ops.combine(wc, xe)
+  probe = torch.randn_like(out)
+  (out.float() * probe.float()).sum().backward()
+  wd2, wc2 = wd.detach().clone().requires_grad_(), wc.detach().clone().requires_grad_()
+  x2 = x.detach().float().requires_grad_()
+  xe2 = torch.einsum("gsn,gsh->gnh", wd2, x2)
+  out2 = torch.einsum("gsn,gnh->gsh", wc2, xe2)
+  (out2 * probe.float()).sum().backward()
+  _close(xe, xe2, 2e-2)
+  _close(out, out2, 2e-2)
+  _close(x.grad, x2.grad, 3e-2)
+  _close(wd.grad, wd2.grad, 3e-2)
+  _close(wc.grad, wc2.grad, 3e-2)

@@ -244,6 +244,11 @@ class MultiHeadDotProductAttention(nn.Module):
       if self.query_ln is None:
         a = ops.attention_packed(qkv, dropout_p=self.dropout_rate, training=self.training)
         return self.out(a.reshape(b, tq, h * d), residual=residual)
+      if not (self.training and self.dropout_rate > 0):
+        # QK-norm: normalise the query and key slices, re-pack and use the fused kernel.
+        qn, kn = self.query_ln(qkv[:, :, 0]), self.key_ln(qkv[:, :, 1])
+        a = ops.attention_packed(torch.stack([qn, kn, qkv[:, :, 2]], dim=2))
+        return self.out(a.reshape(b, tq, h * d), residual=residual)
       q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
     else:
       w, bias = self.qkv.weight, self.qkv.bias

@@ -73,6 +73,11 @@ def _grouped(gates: Tensor) -> Tuple[Tensor, bool]:
   return gates, False
 
 
+def _einsum_ops():
+  from vmoe_b200.ops import einsum_ops
+  return einsum_ops
+
+
 # --------------------------------------------------------------------------------- dispatchers
 class BaseDispatcher:
   """Moves items to experts (``dispatch``) and expert outputs back (``combine``)."""
@@ -142,15 +147,22 @@ class EinsumDispatcher(BaseDispatcher):
     w = self._dispatch_w()
     g, s, e, c = w.shape
     flat = data.reshape(g, s, -1)
-    out = torch.einsum("gsn,gsh->gnh", w.reshape(g, s, e * c).to(flat.dtype), flat)
+    w2 = w.reshape(g, s, e * c)
+    if _einsum_ops().supported(w2, flat):
+      out = _einsum_ops().dispatch(w2 if w2.is_floating_point() else w2.to(flat.dtype), flat)
+    else:
+      out = torch.einsum("gsn,gsh->gnh", w2.to(flat.dtype), flat)
     return _to_experts(out.reshape(g, e, c, *data.shape[2:]), self.exchange)
 
   def combine(self, data: Tensor) -> Tensor:
     g, s, e, c = self.combine_weights.shape
     x = _from_experts(data, g, self.exchange)  # (G, E, C, ...)
     flat = x.reshape(g, e * c, -1)
-    out = torch.einsum("gsn,gnh->gsh", self.combine_weights.reshape(g, s, e * c).to(flat.dtype),
-                       flat)
+    w2 = self.combine_weights.reshape(g, s, e * c)
+    if _einsum_ops().supported(w2, flat):
+      out = _einsum_ops().combine(w2, flat)
+    else:
+      out = torch.einsum("gsn,gnh->gsh", w2.to(flat.dtype), flat)
     return out.reshape(g, s, *x.shape[3:])
 
 
