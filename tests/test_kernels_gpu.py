@@ -271,3 +271,23 @@ def test_einsum_dispatch_combine_on_gemm(g, s, n, h):
   _close(x.grad, x2.grad, 3e-2)
   _close(wd.grad, wd2.grad, 3e-2)
   _close(wc.grad, wc2.grad, 3e-2)
+
+
+def test_linear_with_unaligned_contraction_dim():
+  """K = 588 (14 x 14 x 3 patches) is not a multiple of 8: the op pads it for TMA."""
+  torch.manual_seed(0)
+  x = torch.randn(300, 588, device=DEV).bfloat16().requires_grad_()
+  w = (torch.randn(128, 588, device=DEV) * 0.05).requires_grad_()
+  b = torch.randn(128, device=DEV).requires_grad_()
+  y = ops.linear(x, w, b)
+  dy = torch.randn_like(y)
+  y.backward(dy)
+  x2 = x.detach().float().requires_grad_()
+  w2 = w.detach().bfloat16().float().requires_grad_()
+  b2 = b.detach().clone().requires_grad_()
+  y2 = F.linear(x2, w2, b2)
+  y2.backward(dy.float())
+  _close(y, y2, 2e-2)
+  _close(x.grad, x2.grad, 2e-2)
+  _close(w.grad, w2.grad, 2e-2)
+  _close(b.grad, b2.grad, 2e-2)

@@ -98,6 +98,12 @@ class _LinearFn(torch.autograd.Function):
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
       x2 = x2.contiguous()
+    k_pad = (-x2.shape[1]) % 8
+    if k_pad:
+      # TMA needs 16-byte aligned rows: zero-pad the contraction dim (e.g. 14x14x3 patches).
+      x2 = F.pad(x2, (0, k_pad))
+      w16 = F.pad(w16, (0, k_pad))
+    ctx.k_pad = k_pad
     need_grad = any(ctx.needs_input_grad)
     n = weight.shape[0]
     pre = None
@@ -123,6 +129,9 @@ class _LinearFn(torch.autograd.Function):
     x2, weight, pre = ctx.saved_tensors
     w16 = bf16_shadow(weight)
     n, k = weight.shape
+    k_pad = ctx.k_pad
+    if k_pad:
+      w16 = F.pad(w16, (0, k_pad))
     dy2 = dy.reshape(-1, n)
     if dy2.stride(1) != 1 or dy2.stride(0) % 8:
       n_pad = (n + 7) // 8 * 8
@@ -138,10 +147,19 @@ class _LinearFn(torch.autograd.Function):
     dbias = bias_grad(dy2, ctx.bias) if ctx.has_bias else None  # handles padded rows
     dx = None
     if ctx.needs_input_grad[0]:
-      dx = gemm(dy2, w16, b_mn_major=True).reshape(ctx.x_shape)
+      dx = gemm(dy2, w16, b_mn_major=True)
+      if k_pad:
+        dx = dx[:, :k]
+      dx = dx.reshape(ctx.x_shape)
     dw = None
     if ctx.needs_input_grad[1]:
-      dw = wgrad(dy2, x2, weight, split_k=_wgrad_split(n, k, dy2.shape[0]))
+      if k_pad:
+        full = torch.zeros(n, k + k_pad, dtype=torch.float32, device=dy2.device)
+        gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=full, accumulate=True,
+             split_k=_wgrad_split(n, k, dy2.shape[0]))
+        dw = full[:, :k]
+      else:
+        dw = wgrad(dy2, x2, weight, split_k=_wgrad_split(n, k, dy2.shape[0]))
     return dx, dw, dbias, d_res, None
 
 
