@@ -50,6 +50,41 @@ def main():
       ok = "ValueError"
     json.dump({"result": ok}, open(os.path.join(outdir, f"r{rank}.json"), "w"))
     return
+  if mode in ("peer_stops", "peer_leaves", "barrier_absent"):
+    from vmoe_b200.parallel import failure
+    hb = failure.Heartbeat()
+    result = {}
+    if mode == "barrier_absent":
+      if rank == 0:
+        try:
+          failure.store_barrier("sync", timeout_s=1.5)
+          result["result"] = "no error"
+        except failure.BarrierTimeout as e:
+          result["result"], result["missing"] = "BarrierTimeout", e.missing
+      else:
+        result["result"] = "absent"  # this rank never joins the barrier
+    else:
+      hb.beat(1)
+      hb.check(1, timeout_s=30.0)  # everybody reached step 1
+      if rank == 0:
+        hb.beat(2)
+        try:
+          hb.check(2, timeout_s=1.5)
+          result["result"] = "no error"
+        except failure.PeerFailure as e:
+          result["result"], result["ranks"], result["left"] = "PeerFailure", e.ranks, e.left
+      else:
+        # The failure is made on the host: this rank stops (or leaves) before step 2 and
+        # never publishes it.
+        if mode == "peer_leaves":
+          hb.leave()
+        result["result"] = "stopped"
+    json.dump(result, open(os.path.join(outdir, f"r{rank}.json"), "w"))
+    # Both processes are still alive (the failure was only acted out): leave together so the
+    # store outlives every client.
+    dist.barrier()
+    dist.destroy_process_group()
+    return
   multihost_utils.sync_devices("start")
   state = trainer.create_train_state(
       model_config=small_config(),

@@ -75,3 +75,18 @@ def test_two_ranks_replicated_experts(tmp_path):
 def test_barrier_detects_mismatched_names(tmp_path):
   res = _launch(2, "barrier_mismatch", tmp_path)
   assert all(r["result"] == "ValueError" for r in res)
+
+
+def test_heartbeat_reports_a_rank_that_stops(tmp_path):
+  res = _launch(2, "peer_stops", tmp_path)
+  assert res[0]["result"] == "PeerFailure" and res[0]["ranks"] == [1] and res[0]["left"] == []
+
+
+def test_heartbeat_reports_a_rank_that_leaves(tmp_path):
+  res = _launch(2, "peer_leaves", tmp_path)
+  assert res[0]["result"] == "PeerFailure" and res[0]["left"] == [1]
+
+
+def test_store_barrier_names_the_absent_rank(tmp_path):
+  res = _launch(2, "barrier_absent", tmp_path)
+  assert res[0]["result"] == "BarrierTimeout" and res[0]["missing"] == [1]

@@ -291,3 +291,53 @@ def test_linear_with_unaligned_contraction_dim():
   _close(x.grad, x2.grad, 2e-2)
   _close(w.grad, w2.grad, 2e-2)
   _close(b.grad, b2.grad, 2e-2)
+
+
+def test_wait_counters_times_out_and_reports_status():
+  """A counter that nothing advances: the wait gives up after its limit, sets the peer-timeout
+  bit and the context stays usable."""
+  import ctypes
+  from vmoe_b200.ops import _lib
+  from vmoe_b200.parallel import failure
+  counters = torch.zeros(4, dtype=torch.int32, device=DEV)
+  status = torch.zeros(1, dtype=torch.int32, device=DEV)
+  rc = _lib.lib().vmoe_wait_counters(
+      ctypes.c_void_p(counters.data_ptr()), ctypes.c_int32(4), ctypes.c_uint32(1),
+      ctypes.c_void_p(status.data_ptr()), ctypes.c_int64(200_000_000),
+      ctypes.c_void_p(_lib.stream_ptr()))
+  assert rc == 0
+  torch.cuda.synchronize()
+  assert status.item() & 32
+  with pytest.raises(failure.DeviceWaitTimeout):
+    failure.check_status(status, "wait_counters")
+  assert status.item() == 0
+  assert float((torch.ones(8, device=DEV) * 2).sum()) == 16.0
+
+
+def test_allreduce_range_with_a_peer_that_never_arrives():
+  """The reduce / gather kernels of rank 0 of a pretended 2-rank group whose peer never
+  launches: both waits run out, the status word says so, nothing hangs."""
+  import ctypes
+  from vmoe_b200.ops import _lib
+  n = 8192
+  mine = torch.ones(n, device=DEV)
+  peer = torch.full((n,), 2.0, device=DEV)
+  flags = [torch.zeros(3, dtype=torch.int32, device=DEV) for _ in range(2)]
+  local = torch.zeros(2, dtype=torch.int32, device=DEV)
+  status = torch.zeros(1, dtype=torch.int32, device=DEV)
+  bufs = (ctypes.c_uint64 * 2)(mine.data_ptr(), peer.data_ptr())
+  fl = (ctypes.c_uint64 * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+  rc = _lib.lib().vmoe_allreduce_range(
+      bufs, fl, ctypes.c_int32(2), ctypes.c_int32(0), ctypes.c_int64(0), ctypes.c_int64(n),
+      ctypes.c_int32(0), ctypes.c_int32(1), ctypes.c_uint32(1),
+      ctypes.c_void_p(local.data_ptr()), ctypes.c_void_p(status.data_ptr()), ctypes.c_int32(4),
+      ctypes.c_int64(200_000_000), ctypes.c_void_p(_lib.stream_ptr()))
+  assert rc == 0
+  torch.cuda.synchronize()
+  assert status.item() & 32
+  assert torch.equal(mine, torch.ones(n, device=DEV))  # nothing was reduced
+  # With both "ranks" run in turn (one kernel pair each, epoch 2) the sum is exchanged.
+  status.zero_()
+  for f in flags:
+    f.zero_()
+  local.zero_()
