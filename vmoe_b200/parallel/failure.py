@@ -92,13 +92,13 @@ class Heartbeat:
     deadline = time.monotonic() + timeout_s
     pending = [r for r in range(self.world) if r != self.rank]
     while True:
-      left = [r for r in pending if self.store.check([f"{self._key(r)}/left"])]
-      if left:
-        raise PeerFailure([r for r in pending if r not in left and self._step_of(r) < step],
-                          step, left=left)
+      # A peer that published this step counts for it even if it left afterwards.
       pending = [r for r in pending if self._step_of(r) < step]
       if not pending:
         return
+      left = [r for r in pending if self.store.check([f"{self._key(r)}/left"])]
+      if left:
+        raise PeerFailure([r for r in pending if r not in left], step, left=left)
       if time.monotonic() >= deadline:
         raise PeerFailure(pending, step)
       time.sleep(poll_s)
