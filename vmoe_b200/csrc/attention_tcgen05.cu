@@ -304,12 +304,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         for (int qt = 0; qt < n_qt && ok; ++qt, ++it) {
           const uint32_t qbase = smem_u32(sQ + qt * ATT_TILE_BYTES);
           const uint32_t dobase = smem_u32(sDO + qt * ATT_TILE_BYTES);
-          if (it > 0) {
-            // P/dS smem and S/dP TMEM are free once the previous step's MMAs retired and the
-            // softmax warps consumed S/dP (they arrive on bar_p after their last TMEM read).
-            ATT_WAIT(bar_mma, (it - 1) & 1, kStatusTimeoutMma);
-            if (!ok) break;
-          }
+          // S/dP TMEM is free: the softmax warps arrived on bar_p (waited for below, in the
+          // previous step) after their last TMEM read. No wait for the previous step's
+          // dV/dK/dQ MMAs is needed before issuing: MMAs of one thread execute in order, so
+          // the commit on bar_s below also covers them, and the softmax warps overwrite the
+          // P/dS shared-memory tiles only after bar_s.
           tc_fence_after();
           const uint32_t id_s = umma_idesc_bf16(128, nk, 0, 0);
 #pragma unroll

@@ -3,6 +3,7 @@
   python -m vmoe_b200.ops.bench_kernels <case> [--rows 100864] [--iters 10]
 
 Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with residual),
+``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
 ``layernorm`` (forward and backward), ``attention`` (packed-QKV forward and backward),
 ``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward).
 Every case runs one warm-up pass, then times ``iters`` passes with CUDA events; inputs are
@@ -49,6 +50,31 @@ def gemm_dense(rows: int, iters: int):
   for name, (fn, flops) in cases.items():
     us = _timed(fn, iters)
     print(f"{name}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+
+
+def gemm_dgrad(rows: int, iters: int):
+  """The MLP's hidden-gradient GEMM: dy (rows x 768) x W2 -> rows x 3072, with and without the
+  GELU' multiply and the bias-gradient column sums in the epilogue."""
+  from vmoe_b200.ops import gemm as G
+  from vmoe_b200.ops import reduce
+  dev = "cuda"
+  dy = torch.randn(rows, 768, device=dev).bfloat16()
+  w2 = torch.randn(768, 3072, device=dev).bfloat16()
+  gp = torch.rand(rows, 3072, device=dev).bfloat16()
+  cs = torch.zeros(3072, device=dev)
+  flops = 2 * rows * 768 * 3072
+  out = G.gemm(dy, w2, b_mn_major=True)
+  cases = {
+      "plain": lambda: G.gemm(dy, w2, b_mn_major=True),
+      "gelu_grad": lambda: G.gemm(dy, w2, b_mn_major=True, gelu_pre=gp, gelu_pre_is_grad=True),
+      "colsum": lambda: G.gemm(dy, w2, b_mn_major=True, colsum=cs),
+      "gelu_grad+colsum": lambda: G.gemm(dy, w2, b_mn_major=True, gelu_pre=gp,
+                                         gelu_pre_is_grad=True, colsum=cs),
+      "separate colsum kernel": lambda: reduce.colsum(out, out=cs),
+  }
+  for name, fn in cases.items():
+    us = _timed(fn, iters)
+    print(f"{name}: {us:.1f} us" + (f", {flops / us / 1e6:.0f} TFLOP/s" if "kernel" not in name else ""))
 
 
 def layernorm(rows: int, iters: int):
@@ -103,7 +129,7 @@ def router(rows: int, iters: int):
   print(f"router fwd: {_timed(fwd, iters):.1f} us; fwd+bwd: {_timed(both, iters):.1f} us")
 
 
-CASES = {"gemm_dense": gemm_dense, "layernorm": layernorm, "attention": attention,
+CASES = {"gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad, "layernorm": layernorm, "attention": attention,
          "router": router}
 
 
