@@ -24,6 +24,50 @@ class _Mlp:
   dropout_rate = 0.0
 
 
+def forward_phases(moe_ops, disp, mlp, x, res, ex, c, iters):
+  """The launches of the peer-memory forward (``moe_ops._P2PMoeFn.forward``) with a CUDA event
+  between them; returns mean milliseconds per phase on this rank."""
+  from vmoe_b200.ops.functional import bf16_shadow
+  from vmoe_b200.ops.gemm import ACT_GELU, gemm
+  g, s, h = x.shape
+  e, k = disp.num_experts, disp.expert.shape[-1]
+  r = g * c
+  comm = moe_ops.layer_comm(mlp, ex, e, r, h, x.device)
+  ep, el, rank = comm.ep, comm.el, comm.rank
+  w1h, w2h = bf16_shadow(mlp.w1), bf16_shadow(mlp.w2)
+  gate = disp.combine_weights.detach().float().contiguous()
+  names = ["barrier", "push_rows", "gemm1_gated", "gemm2_to_peers", "signal_wait", "combine"]
+  total = {n: 0.0 for n in names}
+  with torch.no_grad():
+    for it in range(iters + 2):
+      ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+      ev[0].record()
+      comm.buf.barrier()
+      for key in ("x", "y"):
+        comm.epoch[key] += 1
+      ev[1].record()
+      moe_ops.push_rows(x, disp.slot_pair, None, comm.push_x, comm.flag_x, None, None, g, s, e, c,
+                        k, h, el, ep, rank)
+      ev[2].record()
+      hid = gemm(comm.xe, w1h, bias=mlp.b1, act=ACT_GELU, a_ready=comm.fx,
+                 a_ready_epoch=comm.epoch["x"], status=comm.status, mt_offset=comm.mt_offset)
+      ev[3].record()
+      gemm(hid, w2h, bias=mlp.b2, out_multi=[comm.home_out("YB", src) for src in range(ep)])
+      ev[4].record()
+      for src in range(ep):
+        moe_ops.signal(comm.done_flag_addr("FY", src))
+      moe_ops.wait_counters(comm.fy, ep, comm.epoch["y"], comm.status)
+      ev[5].record()
+      out = torch.empty_like(x)
+      moe_ops.combine_rows(comm.yb_table, disp.expert, disp.slot, gate, res, out, g, s, e, c, k, h)
+      ev[6].record()
+      torch.cuda.synchronize()
+      if it >= 2:
+        for i, n in enumerate(names):
+          total[n] += ev[i].elapsed_time(ev[i + 1]) / iters
+  return total
+
+
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--path", default="p2p", choices=["p2p", "nccl"])
@@ -37,6 +81,8 @@ def main():
   ap.add_argument("--gemm-tflops", type=float, default=1418.0,
                   help="measured sustained cuBLAS bf16 throughput used as the compute roof")
   ap.add_argument("--link-gbs", type=float, default=770.0)
+  ap.add_argument("--phases", action="store_true",
+                  help="also time the launches of the peer-memory forward one by one")
   args = ap.parse_args()
   os.environ["VMOE_B200_P2P"] = "1" if args.path == "p2p" else "0"
   from vmoe_b200.ops import moe_ops
@@ -88,6 +134,13 @@ def main():
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
+  if args.phases and args.path == "p2p" and ex.size > 1:
+    phases = forward_phases(moe_ops, disp, mlp, x, res, ex, c, args.iters)
+    t = torch.tensor(list(phases.values()), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+      print(json.dumps({"forward_phases_ms_max_over_ranks":
+                        dict(zip(phases.keys(), [round(v, 4) for v in t.tolist()]))}))
   with torch.no_grad():
     t_fwd = timed(fwd)
   t_both = timed(fwd_bwd)

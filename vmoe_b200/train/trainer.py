@@ -265,6 +265,23 @@ def wrap_train_step_with_adversarial_attack(train_step_fn, loss_fn, *, max_epsil
   return new_train_step_fn
 
 
+def check_device_status(state: TrainState) -> None:
+  """Raises ``failure.DeviceWaitTimeout`` if a kernel of the peer-memory paths (expert exchange,
+  gradient all-reduce) recorded a wait that ran out since the last check. Reading the status
+  words synchronises with the device, so the training loop calls this only every
+  ``check_device_status_every_steps`` steps."""
+  from vmoe_b200.parallel import failure
+  reducer = getattr(state.optimizer, "grad_reducer", None) if state.optimizer else None
+  if reducer is not None:
+    failure.check_status(reducer.status, "gradient all-reduce")
+  try:
+    from vmoe_b200.ops import moe_ops
+  except Exception:  # pylint: disable=broad-except
+    return
+  for comm in getattr(moe_ops, "_LAYER_COMMS", {}).values():
+    failure.check_status(comm.status, "expert exchange")
+
+
 def override_base_config(base, override):
   """Returns ``base`` updated (recursively) with the keys of ``override``."""
   from vmoe_b200.utils.config_dict import ConfigDict
@@ -607,6 +624,7 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
   tr_iter = pjit_utils.prefetch_to_device(
       batches(), size=int(config.dataset.train.get("prefetch_device", 2) or 2), device=device)
 
+  status_every = int(config.get("check_device_status_every_steps", 100) or 100)
   multihost_utils.sync_devices("training:start")
   if init_step == 0 and ckpt_cfg.get("every_steps"):
     ckpt_manager.save(0, state, force=True)
@@ -620,6 +638,8 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
                          microsteps=microsteps, summarizer=summarizer)
     progress_hook(step, scalar_metrics={"train": {k: v for k, v in metrics.items()
                                                   if not isinstance(v, Mapping)}})
+    if step % status_every == 0:
+      check_device_status(state)
     with progress_hook.timed("ckpt", wait_jax_async_dispatch=False):
       ckpt_manager.save(step, state)
     evaluation_hook(step)
