@@ -450,8 +450,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (p.tma_store) {
           // The staging tiles are reused every chunk: wait until the TMA engine has read the
           // previous contents.
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          __syncwarp();
+          if (p.c_multi_rows == 0 || (c & 1) == 0) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+          }
         }
         const bool vec_bf16 = full_cols && (p.ldc % 8 == 0);
         if (p.C2 && p.c2_gelu_grad) {
@@ -584,7 +586,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + i < p.N) v[i] += __bfloat162float(res[i]);
           }
         }
-        if (p.tma_store) {
+        if (p.tma_store && p.c_multi_rows > 0) {
+          // Multi-destination output (possibly peer GPUs over NVLink): two 32-column chunks
+          // share one 32 x 64 staging tile (128-byte rows, 128B swizzle; it spans this warp's
+          // C and C2 staging areas, C2 being unused in this mode) and leave in one store, so
+          // the link sees 128-byte row segments instead of 64-byte ones.
+          const uint32_t cc = static_cast<uint32_t>(c & 1);
+          const uint32_t wrow = static_cast<uint32_t>(lane) * 128u;
+          const uint32_t wxor = static_cast<uint32_t>(lane) & 7u;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+            q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+            q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+            q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+            *reinterpret_cast<uint4*>(stage_c + wrow + (((4u * cc + i) ^ wxor) << 4)) = q;
+          }
+          if (cc == 1 || col0 + 32 >= p.N) {
+            fence_proxy_async();
+            __syncwarp();
+            // Boxes that start past the last row have no destination (and no map): skip them.
+            if (lane == 0) {
+              if (row0 < p.M) {
+                const int j = row0 / p.c_multi_rows;
+                tma_store_3d(&cmaps.m[j], smem_u32(stage_c), col0 - 32 * static_cast<int>(cc),
+                             row0 - j * p.c_multi_rows, t.b);
+              }
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        } else if (p.tma_store) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 q;
@@ -597,17 +629,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           fence_proxy_async();  // make the staged tile visible to the TMA engine
           __syncwarp();
           if (lane == 0) {
-            if (p.c_multi_rows > 0) {
-              // Row block j of the output lives in destination j (possibly a peer GPU's buffer).
-              // Boxes that start past the last row have no destination (and no map): skip them.
-              if (row0 < p.M) {
-                const int j = row0 / p.c_multi_rows;
-                tma_store_3d(&cmaps.m[j], smem_u32(stage_c), col0, row0 - j * p.c_multi_rows,
-                             t.b);
-              }
-            } else {
-              tma_store_3d(&tma_c, smem_u32(stage_c), col0, row0, t.b);
-            }
+            tma_store_3d(&tma_c, smem_u32(stage_c), col0, row0, t.b);
             if (p.C2) tma_store_3d(&tma_c2, smem_u32(stage_c2), col0, row0, t.b);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
@@ -818,12 +840,13 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   CMultiMaps cm = cm_zero;
   int c_multi_rows = 0;
   if (a->c_multi_count > 0) {
-    if (!tma_store || a->C2 != nullptr || a->c_multi_count > MAX_C_DESTS ||
+    if (!tma_store || a->C2 != nullptr || a->residual != nullptr || a->gelu_pre != nullptr ||
+        a->c_multi_count > MAX_C_DESTS ||
         a->c_multi_rows <= 0 || a->c_multi_rows % 32 ||
         a->c_multi_rows * a->c_multi_count < a->M) {
       set_error("%s (code %d)",
-                "multi-destination output needs bf16 TMA stores, no second output, <= 8 "
-                "destinations and a row block that is a multiple of 32", 0);
+                "multi-destination output needs bf16 TMA stores, no second output / residual / "
+                "gelu_pre, <= 8 destinations and a row block that is a multiple of 32", 0);
       return -1;
     }
     for (int j = 0; j < a->c_multi_count; ++j) {
@@ -832,7 +855,7 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
         return -1;
       }
       rc = make_bf16_map(&cm.m[j], a->c_multi[j], a->N, a->c_multi_rows, a->batch, a->ldc,
-                         a->c_batch_stride, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+                         a->c_batch_stride, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc) return rc;
     }
     c_multi_rows = static_cast<int>(a->c_multi_rows);
