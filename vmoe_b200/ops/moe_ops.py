@@ -301,10 +301,7 @@ class _P2PMoeFn(torch.autograd.Function):
                 mt_offset=comm.mt_offset)
     if tgt is not None:
       db1 = None
-    # Every tile of dye has arrived once the GEMM above has run.
-    db2 = bias_grad(comm.dye, b2)
-    dw2 = wgrad(comm.dye, hid, w2)
-    dw1 = wgrad(dpre, comm.xe, w1)
+    # dX first: its tiles travel home over NVLink while the weight-gradient GEMMs below run.
     if r % 32 == 0 and ep <= 8:
       gemm(dpre, w1h, b_mn_major=True,
            out_multi=[comm.home_out("DXB", src) for src in range(ep)])
@@ -316,6 +313,10 @@ class _P2PMoeFn(torch.autograd.Function):
         gemm(dpre[:, src * r:(src + 1) * r], w1h, b_mn_major=True,
              out=comm.home_out("DXB", src))
         signal(comm.done_flag_addr("FDX", src))
+    # Every tile of dye has arrived once the dpre GEMM above has run.
+    db2 = bias_grad(comm.dye, b2)
+    dw2 = wgrad(comm.dye, hid, w2)
+    dw1 = wgrad(dpre, comm.xe, w1)
     wait_counters(comm.fdx, ep, comm.epoch["dx"], comm.status)
     dx = torch.empty(g, s, h, dtype=torch.bfloat16, device=dev)
     combine_rows(comm.dxb_table, expert, slot, None, None, dx, g, s, e, c, k, h)
