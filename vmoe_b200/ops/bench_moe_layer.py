@@ -52,7 +52,8 @@ def forward_phases(moe_ops, disp, mlp, x, res, ex, c, iters):
       hid = gemm(comm.xe, w1h, bias=mlp.b1, act=ACT_GELU, a_ready=comm.fx,
                  a_ready_epoch=comm.epoch["x"], status=comm.status, mt_offset=comm.mt_offset)
       ev[3].record()
-      gemm(hid, w2h, bias=mlp.b2, out_multi=[comm.home_out("YB", src) for src in range(ep)])
+      gemm(hid, w2h, bias=mlp.b2, out_multi=[comm.home_out("YB", src) for src in range(ep)],
+           mt_offset=comm.mt_offset)
       ev[4].record()
       for src in range(ep):
         moe_ops.signal(comm.done_flag_addr("FY", src))

@@ -261,7 +261,10 @@ class _P2PMoeFn(torch.autograd.Function):
     if r % 32 == 0 and ep <= 8:
       # One GEMM over all rows; every 32-row output box is TMA-stored straight into the home
       # buffer of the rank its rows came from.
-      gemm(hid, w2h, bias=b2, out_multi=[comm.home_out("YB", src) for src in range(ep)])
+      # mt_offset: rank r starts with the rows of source r, so at any moment the ranks store to
+      # different destinations instead of all converging on the same GPU's link.
+      gemm(hid, w2h, bias=b2, out_multi=[comm.home_out("YB", src) for src in range(ep)],
+           mt_offset=comm.mt_offset)
       for src in range(ep):
         signal(comm.done_flag_addr("FY", src))
     else:
@@ -304,7 +307,7 @@ class _P2PMoeFn(torch.autograd.Function):
     # dX first: its tiles travel home over NVLink while the weight-gradient GEMMs below run.
     if r % 32 == 0 and ep <= 8:
       gemm(dpre, w1h, b_mn_major=True,
-           out_multi=[comm.home_out("DXB", src) for src in range(ep)])
+           out_multi=[comm.home_out("DXB", src) for src in range(ep)], mt_offset=comm.mt_offset)
       for src in range(ep):
         signal(comm.done_flag_addr("FDX", src))
     else:
