@@ -237,6 +237,146 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
+// ---- short rows (h = 16, 32, 64 or 128: head-dimension LayerNorm of QK-norm attention)
+// LPR = h / 8 lanes hold one row (8 elements each), so a warp normalises 32 / LPR rows at a
+// time and the reductions stay inside the LPR-lane group.
+template <int LPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_small_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                           const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                           float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                           long long rows, float eps) {
+  constexpr int H = LPR * 8, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float gm[8], bt[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    gm[i] = gamma ? __ldg(gamma + l * 8 + i) : 1.f;
+    bt[i] = beta ? __ldg(beta + l * 8 + i) : 0.f;
+  }
+  // All groups of a warp run the same number of iterations (rows past the end are masked out),
+  // so the shuffles always see a full warp.
+  const long long iters = (rows + nwarps * RPW - 1) / (nwarps * RPW);
+  for (long long it = 0; it < iters; ++it) {
+    const long long row = (it * nwarps + warp) * RPW + sub;
+    const bool ok = row < rows;
+    float v[8];
+    if (ok) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(x + row * H) + l), v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+    const float mean = group_sum<LPR>(s) / H;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sq += (v[i] - mean) * (v[i] - mean);
+    const float rstd = rsqrtf(group_sum<LPR>(sq) / H + eps);
+    if (ok) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (v[i] - mean) * rstd * gm[i] + bt[i];
+      reinterpret_cast<uint4*>(y + row * H)[l] = pack8(o);
+      if (l == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
+      }
+    }
+  }
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(128)
+layernorm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                           const float* __restrict__ gamma, const float* __restrict__ mean_in,
+                           const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                           __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
+                           long long rows) {
+  constexpr int H = LPR * 8, RPW = 32 / LPR;
+  extern __shared__ float red[];  // [4 warps][2][H]
+  const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float gm[8], ag[8], ab[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    gm[i] = gamma ? __ldg(gamma + l * 8 + i) : 1.f;
+    ag[i] = ab[i] = 0.f;
+  }
+  // All groups of a warp run the same number of iterations (rows past the end are masked
+  // out), so the shuffles always see a full warp.
+  const long long iters = (rows + nwarps * RPW - 1) / (nwarps * RPW);
+  for (long long it = 0; it < iters; ++it) {
+    const long long row = (it * nwarps + warp) * RPW + sub;
+    const bool ok = row < rows;
+    float xv[8], dv[8];
+    if (ok) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(x + row * H) + l), xv);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(dy + row * H) + l), dv);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = dv[i] = 0.f;
+    }
+    const float mean = ok ? __ldg(mean_in + row) : 0.f, rstd = ok ? __ldg(rstd_in + row) : 0.f;
+    float s1 = 0.f, s2 = 0.f, xh[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      xh[i] = (xv[i] - mean) * rstd;
+      const float g = dv[i] * gm[i];
+      ag[i] += dv[i] * xh[i];
+      ab[i] += dv[i];
+      s1 += g;
+      s2 += g * xh[i];
+    }
+    const float m1 = group_sum<LPR>(s1) / H, m2 = group_sum<LPR>(s2) / H;
+    if (ok) {
+      float o[8], rv[8];
+      if (dres) unpack8(__ldg(reinterpret_cast<const uint4*>(dres + row * H) + l), rv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i] = rstd * (dv[i] * gm[i] - m1 - xh[i] * m2);
+        if (dres) o[i] += rv[i];
+      }
+      reinterpret_cast<uint4*>(dx + row * H)[l] = pack8(o);
+    }
+  }
+  if (partial != nullptr) {
+    // Add the groups of the warp (lanes with equal l), then the four warps in a fixed order.
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int o = LPR; o < 32; o <<= 1) {
+        ag[i] += __shfl_xor_sync(0xffffffffu, ag[i], o);
+        ab[i] += __shfl_xor_sync(0xffffffffu, ab[i], o);
+      }
+    }
+    float* mine = red + (threadIdx.x >> 5) * 2 * H;
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        mine[l * 8 + i] = ag[i];
+        mine[H + l * 8 + i] = ab[i];
+      }
+    }
+    __syncthreads();
+    float* out = partial + static_cast<long long>(blockIdx.x) * 2 * H;
+    for (int i = threadIdx.x; i < 2 * H; i += blockDim.x)
+      out[i] = (red[i] + red[2 * H + i]) + (red[4 * H + i] + red[6 * H + i]);
+  }
+}
+
 // dgamma[j] += sum_b partial[b][j], dbeta[j] += sum_b partial[b][h + j]. Block = 32 columns x
 // 8 row groups; every thread adds a strided subset of the rows in a fixed order and the eight
 // partial results are combined through shared memory, also in a fixed order.
@@ -336,11 +476,25 @@ extern "C" int vmoe_layernorm_fwd(const void* x, const float* gamma, const float
     return -1;
   }
   const int threads = 256;
-  const long long blocks = (rows * 32 + threads - 1) / threads;
-  const int grid = static_cast<int>(blocks < 148 * 2 ? blocks : 148 * 2);
   auto xx = static_cast<const __nv_bfloat16*>(x);
   auto yy = static_cast<__nv_bfloat16*>(y);
   const int chunks = static_cast<int>(h / 8);
+  if (chunks == 2 || chunks == 4 || chunks == 8 || chunks == 16) {
+    // Short rows: several rows per warp.
+    const long long warps = (rows * chunks + 31) / 32;
+    const long long want = (warps * 32 + threads - 1) / threads;
+    const int g = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+#define VMOE_LN_FWD_SMALL(L) layernorm_fwd_small_kernel<L><<<g, threads, 0, stream>>>( \
+      xx, gamma, beta, yy, mean, rstd, rows, eps)
+    if (chunks == 2) VMOE_LN_FWD_SMALL(2);
+    else if (chunks == 4) VMOE_LN_FWD_SMALL(4);
+    else if (chunks == 8) VMOE_LN_FWD_SMALL(8);
+    else VMOE_LN_FWD_SMALL(16);
+#undef VMOE_LN_FWD_SMALL
+    return launch_status("layernorm_fwd");
+  }
+  const long long blocks = (rows * 32 + threads - 1) / threads;
+  const int grid = static_cast<int>(blocks < 148 * 2 ? blocks : 148 * 2);
 #define VMOE_LN_FWD(C) layernorm_fwd_kernel<C><<<grid, threads, 0, stream>>>( \
       xx, gamma, beta, yy, mean, rstd, rows, static_cast<int>(h), eps)
   if (chunks <= 32 * 3) VMOE_LN_FWD(3);
@@ -352,14 +506,21 @@ extern "C" int vmoe_layernorm_fwd(const void* x, const float* gamma, const float
 }
 
 // Number of CTAs the backward kernel uses for `rows` rows (callers size the scratch with it).
-static int ln_bwd_grid(long long rows) {
-  const long long blocks = (rows * 32 + 127) / 128;
+static bool ln_small(long long h) {
+  const long long chunks = h / 8;
+  return h % 8 == 0 && (chunks == 2 || chunks == 4 || chunks == 8 || chunks == 16);
+}
+
+static int ln_bwd_grid(long long rows, long long h = 768) {
+  // Short rows pack 32 / (h / 8) rows into a warp.
+  const long long warps = ln_small(h) ? (rows * (h / 8) + 31) / 32 : rows;
+  const long long blocks = (warps * 32 + 127) / 128;
   const long long cap = 148 * 3;
   return static_cast<int>(blocks < cap ? blocks : cap);
 }
 
 extern "C" int64_t vmoe_layernorm_bwd_scratch_bytes(int64_t rows, int64_t h) {
-  return static_cast<int64_t>(ln_bwd_grid(rows)) * 2 * h * sizeof(float);
+  return static_cast<int64_t>(ln_bwd_grid(rows, h)) * 2 * h * sizeof(float);
 }
 
 namespace vmoe {
@@ -378,7 +539,7 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
     return -1;
   }
   const int threads = 128;
-  const int grid = ln_bwd_grid(rows);
+  const int grid = ln_bwd_grid(rows, h);
   const size_t smem = 4 * 2 * h * sizeof(float);  // one slice per warp (threads / 32 = 4)
   auto a = static_cast<const __nv_bfloat16*>(dy);
   auto b = static_cast<const __nv_bfloat16*>(x);
@@ -386,6 +547,21 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
   auto o = static_cast<__nv_bfloat16*>(dx);
   float* part = want ? scratch : nullptr;
   const int chunks = static_cast<int>(h / 8);
+  if (ln_small(h)) {
+#define VMOE_LN_BWD_SMALL(L) layernorm_bwd_small_kernel<L><<<grid, threads, smem, stream>>>( \
+      a, b, gamma, mean, rstd, r, o, part, rows)
+    if (chunks == 2) VMOE_LN_BWD_SMALL(2);
+    else if (chunks == 4) VMOE_LN_BWD_SMALL(4);
+    else if (chunks == 8) VMOE_LN_BWD_SMALL(8);
+    else VMOE_LN_BWD_SMALL(16);
+#undef VMOE_LN_BWD_SMALL
+    if (want) {
+      const int n = static_cast<int>(2 * h);
+      ln_reduce_partials_kernel<<<(n + 31) / 32, 256, 0, stream>>>(part, grid, static_cast<int>(h),
+                                                                    dgamma, dbeta);
+    }
+    return launch_status("layernorm_bwd");
+  }
 #define VMOE_LN_BWD(C) layernorm_bwd_kernel<C><<<grid, threads, smem, stream>>>( \
       a, b, gamma, mean, rstd, r, o, part, rows, static_cast<int>(h))
   if (chunks <= 32 * 3) VMOE_LN_BWD(3);
@@ -485,7 +661,7 @@ extern "C" int vmoe_layernorm_bwd_static(const void* dy, const void* x, const fl
               static_cast<int>(h));
     return -1;
   }
-  if (ln_bwd_grid(rows) > kLnStaticMaxCtas) {
+  if (ln_bwd_grid(rows, h) > kLnStaticMaxCtas) {
     set_error("%s (code %d)", "layernorm_bwd_static: grid above the static scratch limit", 0);
     return -1;
   }
