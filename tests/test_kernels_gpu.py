@@ -341,3 +341,25 @@ def test_allreduce_range_with_a_peer_that_never_arrives():
   for f in flags:
     f.zero_()
   local.zero_()
+
+
+def test_qk_norm_on_packed_qkv():
+  from vmoe_b200.ops import norm as norm_ops
+  torch.manual_seed(0)
+  b, t, h, d = 3, 50, 4, 64
+  qkv = torch.randn(b, t, 3, h, d, device=DEV).bfloat16().requires_grad_()
+  wq = (torch.rand(d, device=DEV) + 0.5).requires_grad_()
+  wk = (torch.rand(d, device=DEV) + 0.5).requires_grad_()
+  assert norm_ops.qk_norm_packed_supported(qkv, wq, wk, None, None)
+  out = norm_ops.qk_norm_packed(qkv, wq, wk, 1e-6)
+  probe = torch.randn_like(out)
+  out.backward(probe)
+  q2 = qkv.detach().float().requires_grad_()
+  wq2, wk2 = wq.detach().clone().requires_grad_(), wk.detach().clone().requires_grad_()
+  ref = torch.stack([F.layer_norm(q2[:, :, 0], (d,), wq2, None, 1e-6),
+                     F.layer_norm(q2[:, :, 1], (d,), wk2, None, 1e-6), q2[:, :, 2]], dim=2)
+  ref.backward(probe.float())
+  _close(out, ref, 2e-2)
+  _close(qkv.grad, q2.grad, 2e-2)
+  _close(wq.grad, wq2.grad, 1e-2)
+  _close(wk.grad, wk2.grad, 1e-2)

@@ -237,6 +237,17 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
+// Row r of a tensor whose rows come in blocks of `inner` consecutive rows (stride h) with the
+// blocks `outer` elements apart; (inner, outer) = (1, h) is a plain contiguous matrix. Lets the
+// short-row kernels read / write the q or k slice of a packed (B, T, 3, H, D) tensor in place.
+struct RowMap {
+  long long inner, outer;
+  int h;
+  __device__ __forceinline__ long long at(long long r) const {
+    return (r / inner) * outer + (r % inner) * h;
+  }
+};
+
 // ---- short rows (h = 16, 32, 64 or 128: head-dimension LayerNorm of QK-norm attention)
 // LPR = h / 8 lanes hold one row (8 elements each), so a warp normalises 32 / LPR rows at a
 // time and the reductions stay inside the LPR-lane group.
@@ -252,7 +263,7 @@ __global__ void __launch_bounds__(256)
 layernorm_fwd_small_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
                            const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
                            float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                           long long rows, float eps) {
+                           long long rows, float eps, RowMap xm, RowMap ym) {
   constexpr int H = LPR * 8, RPW = 32 / LPR;
   const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -271,7 +282,7 @@ layernorm_fwd_small_kernel(const __nv_bfloat16* __restrict__ x, const float* __r
     const bool ok = row < rows;
     float v[8];
     if (ok) {
-      unpack8(__ldg(reinterpret_cast<const uint4*>(x + row * H) + l), v);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(x + xm.at(row)) + l), v);
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = 0.f;
@@ -288,7 +299,7 @@ layernorm_fwd_small_kernel(const __nv_bfloat16* __restrict__ x, const float* __r
       float o[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] = (v[i] - mean) * rstd * gm[i] + bt[i];
-      reinterpret_cast<uint4*>(y + row * H)[l] = pack8(o);
+      reinterpret_cast<uint4*>(y + ym.at(row))[l] = pack8(o);
       if (l == 0) {
         if (mean_out) mean_out[row] = mean;
         if (rstd_out) rstd_out[row] = rstd;
@@ -303,7 +314,7 @@ layernorm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
                            const float* __restrict__ gamma, const float* __restrict__ mean_in,
                            const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
                            __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
-                           long long rows) {
+                           long long rows, RowMap dym, RowMap xm, RowMap dxm) {
   constexpr int H = LPR * 8, RPW = 32 / LPR;
   extern __shared__ float red[];  // [4 warps][2][H]
   const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
@@ -323,8 +334,8 @@ layernorm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
     const bool ok = row < rows;
     float xv[8], dv[8];
     if (ok) {
-      unpack8(__ldg(reinterpret_cast<const uint4*>(x + row * H) + l), xv);
-      unpack8(__ldg(reinterpret_cast<const uint4*>(dy + row * H) + l), dv);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(x + xm.at(row)) + l), xv);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(dy + dym.at(row)) + l), dv);
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) xv[i] = dv[i] = 0.f;
@@ -349,7 +360,7 @@ layernorm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
         o[i] = rstd * (dv[i] * gm[i] - m1 - xh[i] * m2);
         if (dres) o[i] += rv[i];
       }
-      reinterpret_cast<uint4*>(dx + row * H)[l] = pack8(o);
+      reinterpret_cast<uint4*>(dx + dxm.at(row))[l] = pack8(o);
     }
   }
   if (partial != nullptr) {
@@ -484,8 +495,9 @@ extern "C" int vmoe_layernorm_fwd(const void* x, const float* gamma, const float
     const long long warps = (rows * chunks + 31) / 32;
     const long long want = (warps * 32 + threads - 1) / threads;
     const int g = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+    const RowMap cm{1, h, static_cast<int>(h)};
 #define VMOE_LN_FWD_SMALL(L) layernorm_fwd_small_kernel<L><<<g, threads, 0, stream>>>( \
-      xx, gamma, beta, yy, mean, rstd, rows, eps)
+      xx, gamma, beta, yy, mean, rstd, rows, eps, cm, cm)
     if (chunks == 2) VMOE_LN_FWD_SMALL(2);
     else if (chunks == 4) VMOE_LN_FWD_SMALL(4);
     else if (chunks == 8) VMOE_LN_FWD_SMALL(8);
@@ -548,8 +560,9 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
   float* part = want ? scratch : nullptr;
   const int chunks = static_cast<int>(h / 8);
   if (ln_small(h)) {
+    const RowMap cm{1, h, static_cast<int>(h)};
 #define VMOE_LN_BWD_SMALL(L) layernorm_bwd_small_kernel<L><<<grid, threads, smem, stream>>>( \
-      a, b, gamma, mean, rstd, r, o, part, rows)
+      a, b, gamma, mean, rstd, r, o, part, rows, cm, cm, cm)
     if (chunks == 2) VMOE_LN_BWD_SMALL(2);
     else if (chunks == 4) VMOE_LN_BWD_SMALL(4);
     else if (chunks == 8) VMOE_LN_BWD_SMALL(8);
@@ -636,6 +649,77 @@ extern "C" int vmoe_patchify(const void* img, int32_t img_is_bf16, void* out, in
         static_cast<int>(hh), static_cast<int>(ww), static_cast<int>(c), static_cast<int>(ph),
         static_cast<int>(pw), static_cast<int>(gh), static_cast<int>(gw));
   return launch_status("patchify");
+}
+
+// ------------------------------------------------------------------ short rows inside packed tensors
+// LayerNorm over rows of h = 16 / 32 / 64 / 128 elements that are laid out as blocks of `inner`
+// consecutive rows, the blocks `*_outer` elements apart (e.g. the q slice of a packed
+// (B, T, 3, H, D) projection: inner = H, outer = 3 * H * D).
+extern "C" int vmoe_layernorm_fwd_strided(const void* x, const float* gamma, const float* beta,
+                                          void* y, float* mean, float* rstd, int64_t rows,
+                                          int64_t h, float eps, int64_t inner, int64_t x_outer,
+                                          int64_t y_outer, vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows == 0) return 0;
+  if (!ln_small(h) || inner < 1 || x_outer % 8 || y_outer % 8) {
+    set_error("%s (code %d)", "layernorm_strided: h must be 16/32/64/128, outer strides % 8 == 0", 0);
+    return -1;
+  }
+  const int threads = 256, chunks = static_cast<int>(h / 8);
+  const long long warps = (rows * chunks + 31) / 32;
+  const long long want = (warps * 32 + threads - 1) / threads;
+  const int g = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+  const RowMap xm{inner, x_outer, static_cast<int>(h)}, ym{inner, y_outer, static_cast<int>(h)};
+  auto xx = static_cast<const __nv_bfloat16*>(x);
+  auto yy = static_cast<__nv_bfloat16*>(y);
+#define VMOE_LN_FWD_SMALL(L) layernorm_fwd_small_kernel<L><<<g, threads, 0, stream>>>( \
+      xx, gamma, beta, yy, mean, rstd, rows, eps, xm, ym)
+  if (chunks == 2) VMOE_LN_FWD_SMALL(2);
+  else if (chunks == 4) VMOE_LN_FWD_SMALL(4);
+  else if (chunks == 8) VMOE_LN_FWD_SMALL(8);
+  else VMOE_LN_FWD_SMALL(16);
+#undef VMOE_LN_FWD_SMALL
+  return launch_status("layernorm_fwd_strided");
+}
+
+extern "C" int vmoe_layernorm_bwd_strided(const void* dy, const void* x, const float* gamma,
+                                          const float* mean, const float* rstd, void* dx,
+                                          float* dgamma, float* dbeta, float* scratch,
+                                          int64_t rows, int64_t h, int64_t inner, int64_t dy_outer,
+                                          int64_t x_outer, int64_t dx_outer,
+                                          vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows == 0) return 0;
+  if (!ln_small(h) || inner < 1 || dy_outer % 8 || x_outer % 8 || dx_outer % 8) {
+    set_error("%s (code %d)", "layernorm_strided: h must be 16/32/64/128, outer strides % 8 == 0", 0);
+    return -1;
+  }
+  const bool want = dgamma != nullptr || dbeta != nullptr;
+  if (want && scratch == nullptr) {
+    set_error("%s (code %d)", "layernorm_bwd_strided: scratch buffer required", 0);
+    return -1;
+  }
+  const int threads = 128, chunks = static_cast<int>(h / 8);
+  const int grid = ln_bwd_grid(rows, h);
+  const size_t smem = 4 * 2 * h * sizeof(float);
+  const int hh = static_cast<int>(h);
+  const RowMap dym{inner, dy_outer, hh}, xm{inner, x_outer, hh}, dxm{inner, dx_outer, hh};
+  auto a = static_cast<const __nv_bfloat16*>(dy);
+  auto b = static_cast<const __nv_bfloat16*>(x);
+  auto o = static_cast<__nv_bfloat16*>(dx);
+  float* part = want ? scratch : nullptr;
+#define VMOE_LN_BWD_SMALL(L) layernorm_bwd_small_kernel<L><<<grid, threads, smem, stream>>>( \
+      a, b, gamma, mean, rstd, nullptr, o, part, rows, dym, xm, dxm)
+  if (chunks == 2) VMOE_LN_BWD_SMALL(2);
+  else if (chunks == 4) VMOE_LN_BWD_SMALL(4);
+  else if (chunks == 8) VMOE_LN_BWD_SMALL(8);
+  else VMOE_LN_BWD_SMALL(16);
+#undef VMOE_LN_BWD_SMALL
+  if (want) {
+    const int n = static_cast<int>(2 * h);
+    ln_reduce_partials_kernel<<<(n + 31) / 32, 256, 0, stream>>>(part, grid, hh, dgamma, dbeta);
+  }
+  return launch_status("layernorm_bwd_strided");
 }
 
 // ------------------------------------------------------------------ no-allocation LayerNorm backward

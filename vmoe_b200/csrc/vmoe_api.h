@@ -78,6 +78,19 @@ VMOE_API int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamm
                                 const float* mean, const float* rstd, const void* dres, void* dx,
                                 float* dgamma, float* dbeta, float* scratch, int64_t rows,
                                 int64_t h, vmoe_stream_t stream);
+// LayerNorm over short rows (h = 16, 32, 64 or 128) that sit inside a larger tensor as blocks
+// of `inner` consecutive rows, the blocks `*_outer` elements apart: row r starts at
+// (r / inner) * outer + (r % inner) * h. Used on the q / k slices of a packed QKV projection.
+VMOE_API int vmoe_layernorm_fwd_strided(const void* x, const float* gamma, const float* beta,
+                                        void* y, float* mean, float* rstd, int64_t rows,
+                                        int64_t h, float eps, int64_t inner, int64_t x_outer,
+                                        int64_t y_outer, vmoe_stream_t stream);
+VMOE_API int vmoe_layernorm_bwd_strided(const void* dy, const void* x, const float* gamma,
+                                        const float* mean, const float* rstd, void* dx,
+                                        float* dgamma, float* dbeta, float* scratch, int64_t rows,
+                                        int64_t h, int64_t inner, int64_t dy_outer,
+                                        int64_t x_outer, int64_t dx_outer, vmoe_stream_t stream);
+
 // No-allocation variant of vmoe_layernorm_bwd (this entry point has no counterpart in the
 // reference, which leaves all memory management to XLA). The partial sums of dgamma / dbeta go
 // to a static device array inside the library (3.5 MiB, hidden sizes up to 1024) instead of a

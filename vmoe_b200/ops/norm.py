@@ -108,3 +108,72 @@ def layer_norm_fork(x, weight, bias, eps=1e-6):
   """Returns ``(LayerNorm(x), x)``; use the second value for the residual connection."""
   assert weight is None or weight.dtype == torch.float32
   return _LayerNormForkFn.apply(x, weight, bias, eps)
+
+
+class _QKNormPackedFn(torch.autograd.Function):
+  """LayerNorm over the head dimension of the q and k slices of a packed ``(B, T, 3, H, D)``
+  projection, written straight into a new packed tensor (v is copied). The kernels address the
+  slices in place, so neither direction materialises contiguous copies of q / k or re-stacks
+  the result."""
+
+  @staticmethod
+  def forward(ctx, qkv, wq, wk, eps):
+    b, t, three, h, d = qkv.shape
+    assert three == 3 and qkv.is_contiguous()
+    out = torch.empty_like(qkv)
+    rows = b * t * h
+    outer = 3 * h * d
+    stats = torch.empty(4, rows, dtype=torch.float32, device=qkv.device)
+    lib = _lib.lib()
+    es = qkv.element_size()
+    for i, w in enumerate((wq, wk)):
+      rc = lib.vmoe_layernorm_fwd_strided(
+          _vp(qkv.data_ptr() + i * h * d * es), _vp(_lib.ptr(w)), _vp(None),
+          _vp(out.data_ptr() + i * h * d * es), _vp(stats[2 * i].data_ptr()),
+          _vp(stats[2 * i + 1].data_ptr()), ctypes.c_int64(rows), ctypes.c_int64(d),
+          ctypes.c_float(eps), ctypes.c_int64(h), ctypes.c_int64(outer), ctypes.c_int64(outer),
+          _vp(_lib.stream_ptr()))
+      _lib.check(rc, "vmoe_layernorm_fwd_strided")
+    _lib.count_launch(2)
+    out[:, :, 2].copy_(qkv[:, :, 2])
+    ctx.save_for_backward(qkv, wq, wk, stats)
+    return out
+
+  @staticmethod
+  def backward(ctx, dout):
+    qkv, wq, wk, stats = ctx.saved_tensors
+    b, t, _, h, d = qkv.shape
+    dout = dout.contiguous()
+    dqkv = torch.empty_like(qkv)
+    rows, outer, es = b * t * h, 3 * h * d, qkv.element_size()
+    lib = _lib.lib()
+    lib.vmoe_layernorm_bwd_scratch_bytes.restype = ctypes.c_int64
+    nbytes = lib.vmoe_layernorm_bwd_scratch_bytes(ctypes.c_int64(rows), ctypes.c_int64(d))
+    scratch = torch.empty(max(int(nbytes) // 4, 1), dtype=torch.float32, device=qkv.device)
+    grads = []
+    for i, w in enumerate((wq, wk)):
+      buf, ret = _grad_or_new(w, d, qkv.device)
+      rc = lib.vmoe_layernorm_bwd_strided(
+          _vp(dout.data_ptr() + i * h * d * es), _vp(qkv.data_ptr() + i * h * d * es),
+          _vp(_lib.ptr(w)), _vp(stats[2 * i].data_ptr()), _vp(stats[2 * i + 1].data_ptr()),
+          _vp(dqkv.data_ptr() + i * h * d * es), _vp(_lib.ptr(buf)), _vp(None),
+          _vp(scratch.data_ptr()), ctypes.c_int64(rows), ctypes.c_int64(d), ctypes.c_int64(h),
+          ctypes.c_int64(outer), ctypes.c_int64(outer), ctypes.c_int64(outer),
+          _vp(_lib.stream_ptr()))
+      _lib.check(rc, "vmoe_layernorm_bwd_strided")
+      grads.append(ret)
+    _lib.count_launch(4)
+    dqkv[:, :, 2].copy_(dout[:, :, 2])
+    return dqkv, grads[0], grads[1], None
+
+
+def qk_norm_packed_supported(qkv, wq, wk, bias_q, bias_k) -> bool:
+  return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 5 and qkv.shape[2] == 3
+          and qkv.shape[-1] in (16, 32, 64, 128) and qkv.is_contiguous() and bias_q is None
+          and bias_k is None and wq is not None and wk is not None
+          and wq.dtype == torch.float32 and wk.dtype == torch.float32)
+
+
+def qk_norm_packed(qkv, wq, wk, eps=1e-6):
+  """Packed ``(B, T, 3, H, D)`` with LayerNorm (scale only) applied to q and k per head."""
+  return _QKNormPackedFn.apply(qkv, wq, wk, eps)
