@@ -363,3 +363,25 @@ def test_qk_norm_on_packed_qkv():
   _close(qkv.grad, q2.grad, 2e-2)
   _close(wq.grad, wq2.grad, 1e-2)
   _close(wk.grad, wk2.grad, 1e-2)
+
+
+def test_soft_router_fast_logits_match_reference_path():
+  from vmoe_b200.projects.soft_moe import router as soft_router
+  torch.manual_seed(0)
+  r = soft_router.SoftRouter(num_experts=16, hidden_size=64, num_slots=1,
+                             compute_similarity_metrics=False).to(DEV)
+  r.eval()
+  x = torch.randn(4, 50, 64, device=DEV).bfloat16().requires_grad_()
+  d1, _ = r(x)
+  w1 = d1.dispatcher.combine_weights
+  w1.square().sum().backward()
+  g1, gm1 = x.grad.clone(), r.mu.grad.clone()
+  x.grad = None
+  r.mu.grad = None
+  with ops.use_cuda_kernels(False):
+    d2, _ = r(x)
+  w2 = d2.dispatcher.combine_weights
+  w2.square().sum().backward()
+  _close(w1, w2, 2e-2)
+  _close(g1, x.grad, 5e-2)
+  _close(gm1, r.mu.grad, 5e-2)

@@ -79,8 +79,7 @@ class SoftRouter(nn.Module):
     dtype = self.dtype or inputs.dtype
     if dtype == torch.bfloat16:
       dtype = torch.float32  # routing statistics in fp32; payloads travel in bf16
-    x = normalize(inputs.to(dtype), axis=-1)
-    _, group_size, dim = x.shape
+    _, group_size, dim = inputs.shape
     if self.num_slots is None:
       slots = moe.compute_capacity(group_size, self.num_experts, self.capacity_factor,
                                    ceil_or_round="round", multiple_of=1)
@@ -92,11 +91,14 @@ class SoftRouter(nn.Module):
       raise ValueError(f"mu was created for {self.mu.shape[2]} slots but {slots} are needed")
     mu = normalize(self.mu.to(dtype), axis=0)
     scale = self.scale.to(dtype)
-    if x.numel() < mu.numel():
-      x = x * scale
-    else:
-      mu = mu * scale
-    logits = torch.einsum("gmd,dnp->gmnp", x, mu)
+    logits = self._fast_logits(inputs, mu, scale)
+    if logits is None:
+      x = normalize(inputs.to(dtype), axis=-1)
+      if x.numel() < mu.numel():
+        x = x * scale
+      else:
+        mu = mu * scale
+      logits = torch.einsum("gmd,dnp->gmnp", x, mu)
     if not self.is_deterministic() and self.noise_std > 0:
       logits = logits + self.noise_std * torch.randn_like(logits)
     dispatch_weights = torch.softmax(logits, dim=1)
@@ -106,6 +108,22 @@ class SoftRouter(nn.Module):
         combine_weights=combine_weights, dispatch_weights=dispatch_weights,
         exchange=self.exchange))
     return dispatcher, self.get_metrics(combine_weights, dispatch_weights, mu)
+
+  def _fast_logits(self, inputs: Tensor, mu: Tensor, scale: Tensor) -> Optional[Tensor]:
+    """``<normalize(x), mu> * scale`` for bf16 CUDA activations without materialising the
+    normalised tokens: the raw ``x @ mu`` runs on the tensor-core GEMM (fp32 accumulation and
+    output) and the per-token ``rsqrt(|x|^2 + eps)`` scales the rows of the (much smaller)
+    logits afterwards. Returns None when the fast path does not apply."""
+    from vmoe_b200.ops import router_ops
+    d, n, p = mu.shape
+    if not (inputs.is_cuda and inputs.dtype == torch.bfloat16 and (n * p) % 8 == 0 and d % 8 == 0
+            and router_ops.gating_logits_supported(inputs, mu.reshape(d, n * p).t())):
+      return None
+    w = mu.reshape(d, n * p).t().contiguous()  # (slots, hidden)
+    raw = router_ops.gating_logits(inputs, w)  # (G, S, n * p) fp32
+    norm = torch.linalg.vector_norm(inputs, ord=2, dim=-1, keepdim=True, dtype=torch.float32)
+    inv = torch.rsqrt(norm * norm + 1e-6)
+    return (raw * (inv * scale)).reshape(*raw.shape[:2], n, p)
 
   def get_metrics(self, combine_weights: Tensor, dispatch_weights: Tensor, mu: Tensor):
     g, m, n, p = combine_weights.shape
