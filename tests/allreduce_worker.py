@@ -46,6 +46,11 @@ def run(mesh, device, use_p2p, rank, steps=3):
 
 def main():
   logging.disable(logging.WARNING)
+  watchdog = int(os.environ.get("WORKER_WATCHDOG_S", "0"))
+  if watchdog:
+    # Dump every thread's Python stack and exit if the worker is still running by then.
+    import faulthandler
+    faulthandler.dump_traceback_later(watchdog, exit=True)
   outdir = sys.argv[1]
   mesh_lib.init_distributed()
   rank, world = dist.get_rank(), dist.get_world_size()

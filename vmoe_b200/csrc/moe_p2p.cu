@@ -61,7 +61,11 @@ __device__ __forceinline__ uint4 pack8p(const float (&f)[8]) {
   return q;
 }
 
-__global__ void __launch_bounds__(256)
+// 128 threads and at most 48 registers per thread: small enough to be co-resident with one
+// 320-thread GEMM CTA on every SM, so a push on a side stream makes progress while an
+// arrival-gated GEMM occupies all SMs.
+constexpr int PUSH_THREADS = 128;
+__global__ void __launch_bounds__(PUSH_THREADS)
 push_rows_kernel(const PushParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunks = p.h >> 3;
@@ -78,7 +82,7 @@ push_rows_kernel(const PushParams p) {
     const int j0 = (rem % chunks_per_expert) * PUSH_ROWS;  // first row of the chunk in the block
     const int nrows = min(PUSH_ROWS, block_rows - j0);
     __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(p.dst_base[ee]);
-    for (int jj = warp; jj < nrows; jj += 8) {
+    for (int jj = warp; jj < nrows; jj += PUSH_THREADS / 32) {
       const int j = j0 + jj;
       const int gi = j / p.c, ci = j - gi * p.c;
       const int pair = __ldg(p.slot_pair + (static_cast<long long>(gi) * p.e + ee) * p.c + ci);
@@ -195,8 +199,8 @@ extern "C" int vmoe_moe_push_rows(const void* x, const int32_t* slot_pair, const
   p.row0 = static_cast<int>(rank * groups * c);
   const long long block_rows = groups * c;
   const long long total = e * ((block_rows + PUSH_ROWS - 1) / PUSH_ROWS);
-  const int grid = static_cast<int>(total < 148 * 4 ? total : 148 * 4);
-  push_rows_kernel<<<grid, 256, 0, stream>>>(p);
+  const int grid = static_cast<int>(total < 148 * 8 ? total : 148 * 8);
+  push_rows_kernel<<<grid, PUSH_THREADS, 0, stream>>>(p);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("%s (code %d)", cudaGetErrorString(err), static_cast<int>(err));
