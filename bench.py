@@ -62,7 +62,7 @@ def reference_arm(args) -> int:
     why = "reference importable but no runner is wired up"
   except Exception as e:  # pylint: disable=broad-except
     why = (f"reference not installable offline: {type(e).__name__}: {e}; jax/flax/optax/clu/"
-           "tensorflow are absent from the image and the wheelhouse, and /root/reference has no "
+           "tensorflow are absent from the image and the wheelhouse, and the reference tree has no "
            "setup.py or pyproject.toml")
   if int(os.environ.get("RANK", "0")) == 0:
     print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
