@@ -142,7 +142,7 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
 // (ln_reduce_partials_kernel) sums the rows of `partial` into dgamma / dbeta, so the result
 // does not depend on the order in which CTAs finish.
 template <int MAXC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, MAXC <= 3 ? 3 : 1)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
@@ -153,60 +153,83 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const int chunks = h >> 3;
-  float gm[MAXC][8];
-  ln_load_affine<MAXC>(gamma, lane, chunks, 1.0f, gm);
-  float ag[MAXC][8], ab[MAXC][8];
+  // All per-element arithmetic works on fp32 pairs (one instruction per two values).
+  f32x2 gm[MAXC][4], ag[MAXC][4], ab[MAXC][4];
+  {
+    float g1[MAXC][8];
+    ln_load_affine<MAXC>(gamma, lane, chunks, 1.0f, g1);
 #pragma unroll
-  for (int c = 0; c < MAXC; ++c)
+    for (int c = 0; c < MAXC; ++c)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ag[c][i] = ab[c][i] = 0.f;
-  uint4 xc[MAXC], dc[MAXC], xn[MAXC], dn[MAXC];
+      for (int j = 0; j < 4; ++j) {
+        gm[c][j] = f2_pack(g1[c][2 * j], g1[c][2 * j + 1]);
+        ag[c][j] = ab[c][j] = f2_pack(0.f, 0.f);
+      }
+  }
+  uint4 xc[MAXC], dc[MAXC], xn[MAXC], dn[MAXC], rc[MAXC];
   if (warp < rows) {
     ln_load_row<MAXC>(x, warp, h, lane, chunks, xc);
     ln_load_row<MAXC>(dy, warp, h, lane, chunks, dc);
   }
+  auto pair_of = [](uint32_t u) {
+    const float2 f = unpack_bf16x2(u);
+    return f2_pack(f.x, f.y);
+  };
   for (long long row = warp; row < rows; row += nwarps) {
+    // The residual gradient of this row is requested first, then the next row's x / dy: all
+    // of it is in flight while the sums below are formed.
+    if (dres) ln_load_row<MAXC>(dres, row, h, lane, chunks, rc);
     if (row + nwarps < rows) {
       ln_load_row<MAXC>(x, row + nwarps, h, lane, chunks, xn);
       ln_load_row<MAXC>(dy, row + nwarps, h, lane, chunks, dn);
     }
     const float mean = __ldg(mean_in + row), rstd = __ldg(rstd_in + row);
-    float s1 = 0.f, s2 = 0.f;
+    const f32x2 rstd2 = f2_pack(rstd, rstd), nmr2 = f2_pack(-mean * rstd, -mean * rstd);
+    f32x2 s1 = f2_pack(0.f, 0.f), s2 = f2_pack(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       if (lane + 32 * c < chunks) {
-        float xv[8], dv[8];
-        unpack8(xc[c], xv);
-        unpack8(dc[c], dv);
+        const uint32_t xw[4] = {xc[c].x, xc[c].y, xc[c].z, xc[c].w};
+        const uint32_t dw[4] = {dc[c].x, dc[c].y, dc[c].z, dc[c].w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float xh = (xv[i] - mean) * rstd;
-          const float g = dv[i] * gm[c][i];
-          ag[c][i] += dv[i] * xh;
-          ab[c][i] += dv[i];
-          s1 += g;
-          s2 += g * xh;
+        for (int j = 0; j < 4; ++j) {
+          const f32x2 xh = f2_fma(pair_of(xw[j]), rstd2, nmr2);  // (x - mean) * rstd
+          const f32x2 d = pair_of(dw[j]);
+          const f32x2 g = f2_mul(d, gm[c][j]);
+          ag[c][j] = f2_fma(d, xh, ag[c][j]);
+          ab[c][j] = f2_add(ab[c][j], d);
+          s1 = f2_add(s1, g);
+          s2 = f2_fma(g, xh, s2);
         }
       }
     }
-    const float m1 = warp_sum(s1) / h, m2 = warp_sum(s2) / h;
+    float s1a, s1b, s2a, s2b;
+    f2_unpack(s1, s1a, s1b);
+    f2_unpack(s2, s2a, s2b);
+    const float m1 = warp_sum(s1a + s1b) / h, m2 = warp_sum(s2a + s2b) / h;
+    const f32x2 nm1 = f2_pack(-m1, -m1), nm2 = f2_pack(-m2, -m2);
     uint4* dxr = reinterpret_cast<uint4*>(dx + row * h);
-    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + row * h) : nullptr;
+    const bool rr = dres != nullptr;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = lane + 32 * c;
       if (ch < chunks) {
-        float xv[8], dv[8], o[8], rv[8];
-        unpack8(xc[c], xv);
-        unpack8(dc[c], dv);
-        if (rr) unpack8(__ldg(rr + ch), rv);
+        const uint32_t xw[4] = {xc[c].x, xc[c].y, xc[c].z, xc[c].w};
+        const uint32_t dw[4] = {dc[c].x, dc[c].y, dc[c].z, dc[c].w};
+        const uint32_t rw[4] = {rc[c].x, rc[c].y, rc[c].z, rc[c].w};
+        uint32_t ow[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float xh = (xv[i] - mean) * rstd;
-          o[i] = rstd * (dv[i] * gm[c][i] - m1 - xh * m2);
-          if (rr) o[i] += rv[i];
+        for (int j = 0; j < 4; ++j) {
+          const f32x2 xh = f2_fma(pair_of(xw[j]), rstd2, nmr2);
+          const f32x2 g = f2_mul(pair_of(dw[j]), gm[c][j]);
+          // rstd * (g - m1 - xh * m2) (+ residual gradient)
+          f32x2 o = f2_mul(f2_add(f2_fma(xh, nm2, g), nm1), rstd2);
+          if (rr) o = f2_add(o, pair_of(rw[j]));
+          float oa, ob;
+          f2_unpack(o, oa, ob);
+          ow[j] = pack_bf16x2(oa, ob);
         }
-        dxr[ch] = pack8(o);
+        dxr[ch] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
       }
     }
 #pragma unroll
@@ -224,9 +247,14 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       const int ch = lane + 32 * c;
       if (ch < chunks) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          mine[ch * 8 + i] = ag[c][i];
-          mine[h + ch * 8 + i] = ab[c][i];
+        for (int j = 0; j < 4; ++j) {
+          float a0, a1, b0, b1;
+          f2_unpack(ag[c][j], a0, a1);
+          f2_unpack(ab[c][j], b0, b1);
+          mine[ch * 8 + 2 * j] = a0;
+          mine[ch * 8 + 2 * j + 1] = a1;
+          mine[h + ch * 8 + 2 * j] = b0;
+          mine[h + ch * 8 + 2 * j + 1] = b1;
         }
       }
     }

@@ -86,13 +86,13 @@ def layernorm(rows: int, iters: int):
   g = torch.randn_like(y)
   us_f = _timed(lambda: ops.layer_norm(x, w, b, 1e-6), iters)
 
-  def both():
-    ops.layer_norm(x, w, b, 1e-6).backward(g)
-
-  us_fb = _timed(both, iters)
   nbytes = rows * 768 * 2
+  us_b = _timed(lambda: torch.autograd.grad(y, x, g, retain_graph=True), iters)
+  y2, xr = ops.layer_norm_fork(x, w, b, 1e-6)
+  us_bf = _timed(lambda: torch.autograd.grad([y2, xr], x, [g, g], retain_graph=True), iters)
   print(f"layernorm fwd: {us_f:.1f} us ({2 * nbytes / us_f / 1e3:.0f} GB/s); "
-        f"fwd+bwd: {us_fb:.1f} us")
+        f"bwd: {us_b:.1f} us ({3 * nbytes / us_b / 1e3:.0f} GB/s); "
+        f"bwd with residual gradient: {us_bf:.1f} us ({4 * nbytes / us_bf / 1e3:.0f} GB/s)")
 
 
 def attention(rows: int, iters: int):
