@@ -1,0 +1,47 @@
+"""The training CLI end to end on CPU: config file, ``--config.x.y=v`` overrides, workdir."""
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CONFIG = '''
+from vmoe_b200.configs.vmoe_paper import common
+from vmoe_b200.utils.config_dict import ConfigDict
+
+
+def get_config():
+  config = common.get_base_config()
+  pp = 'value_range(-1,1)|onehot(10, inkey="label", outkey="labels")|keep("image", "labels")'
+  config.dataset = ConfigDict(type_safe=False)
+  for variant, split in (("train", "train"), ("val", "validation[:16]")):
+    d = common.get_data_config(name="synthetic", split=split, batch_size=8, process=pp)
+    d.image_size, d.num_classes = 32, 10
+    setattr(config.dataset, variant, d)
+  config.train_steps = 5
+  config.loss = ConfigDict({"name": "softmax_xent"})
+  config.optimizer = common.get_optimizer_config("ViT-S/32, E=8, K=2, Last 2")
+  config.model = common.get_vmoe_config("ViT-S/32, E=8, K=2, Last 2", 32, 10)
+  config.model.encoder.num_layers = 2
+  config.model.encoder.moe.layers = (1,)
+  config.model.encoder.moe.group_size = 8
+  config.evaluate.every_steps = 2
+  config.save_checkpoint.every_steps = 2
+  config.extra_rng_keys = ("dropout", "gating")
+  return config
+'''
+
+
+def test_train_main_with_config_file_and_overrides(tmp_path):
+  cfg = tmp_path / "cfg.py"
+  cfg.write_text(CONFIG)
+  workdir = tmp_path / "run"
+  env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
+  res = subprocess.run(
+      [sys.executable, "-m", "vmoe_b200.train.main", f"--config={cfg}", f"--workdir={workdir}",
+       "--config.train_steps=2", "--config.optimizer.learning_rate.peak_value=0.001"],
+      cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+  assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+  files = os.listdir(workdir / "ckpt")
+  assert any(f.startswith("ckpt_2.index") for f in files), files  # the override took effect
+  assert "val/prec@1" in res.stderr or "val/prec@1" in res.stdout

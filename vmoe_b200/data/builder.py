@@ -206,7 +206,14 @@ class TfdsBuilder(DatasetBuilder):
     return self._builder().info.splits[self.split].num_examples
 
   def as_dataset(self):
-    import tensorflow_datasets as tfds
+    try:
+      import tensorflow_datasets as tfds
+    except ImportError as e:
+      raise ImportError(
+          f"dataset {self.name!r} is read through tensorflow_datasets, which is not installed; "
+          "use name='synthetic' (random images / labels of the configured shape) or "
+          "name='arrays' (NumPy .npz files), e.g. --config.dataset.<variant>.name=synthetic"
+      ) from e
     split = tfds.split_for_jax_process(self.split, drop_remainder=False)
     data = self._builder().as_dataset(
         split=split, decoders={"image": tfds.decode.SkipDecoding()},
