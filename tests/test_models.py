@@ -161,3 +161,24 @@ def test_initialize_from_vmoe_drops_head_and_zooms_position_embedding(tmp_path):
   a = src.Encoder.encoderblock_0.SelfAttention.qkv.weight
   b = dst.Encoder.encoderblock_0.SelfAttention.qkv.weight
   assert torch.allclose(a, b)
+
+
+def test_forward_flop_count_of_a_tiny_vit_moe():
+  from vmoe_b200.utils import misc
+  mesh = _mesh()
+  model = models_lib.create_model(_vmoe_cfg(), mesh=mesh, image_size=16)
+  b, t, h, m, classes = 4, 5, 32, 64, 7
+  rows = b * t
+  embed = 2 * b * 4 * (8 * 8 * 3) * h
+  attn = 2 * (2 * rows * h * 3 * h + 4 * b * 4 * t * t * (h // 4) + 2 * rows * h * h)
+  dense_mlp = 2 * rows * 2 * h * m
+  # MoE block: 2 groups of 10 tokens, 4 experts, K=2, capacity factor 2 -> C = 10 (-> mult of 4: 12)
+  from vmoe_b200 import moe
+  cap = moe.compute_capacity(10 * 2, 4, 2.0, "ceil", 4)
+  moe_mlp = 2 * (2 * 4 * cap) * 2 * h * m + 2 * rows * h * 4
+  head = 2 * b * h * classes
+  want = embed + attn + dense_mlp + moe_mlp + head
+  got = misc.count_forward_flops(model, torch.rand(b, 16, 16, 3))
+  assert got == pytest.approx(want, rel=1e-6), (got, want)
+  flops, secs = misc.get_flops_and_seconds_per_device(model, torch.rand(b, 16, 16, 3))
+  assert flops == pytest.approx(3 * want) and secs == pytest.approx(flops / 1.418e15)

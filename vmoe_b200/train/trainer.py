@@ -282,6 +282,22 @@ def check_device_status(state: TrainState) -> None:
     failure.check_status(comm.status, "expert exchange")
 
 
+def make_train_cost_fn(flops_per_device: Optional[float], seconds_per_device: Optional[float],
+                       num_devices: int = 1) -> Callable[[int], Dict[str, float]]:
+  """Returns ``fn(step) -> {'flops': ..., 'device_seconds': ...}``: the total training cost up
+  to ``step`` over all devices (``vmoe/train/trainer.py:539-553`` of the reference)."""
+
+  def fn(step: int) -> Dict[str, float]:
+    out: Dict[str, float] = {}
+    if flops_per_device is not None:
+      out["flops"] = flops_per_device * step * num_devices
+    if seconds_per_device is not None:
+      out["device_seconds"] = seconds_per_device * step * num_devices
+    return out
+
+  return fn
+
+
 def override_base_config(base, override):
   """Returns ``base`` updated (recursively) with the keys of ``override``."""
   from vmoe_b200.utils.config_dict import ConfigDict
@@ -630,13 +646,22 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
     ckpt_manager.save(0, state, force=True)
   t_start = time.time()
   metrics = {}
+  train_cost_fn = None
   for step in range(init_step + 1, train_steps + 1):
     batch = next(tr_iter)
+    if train_cost_fn is None:
+      try:
+        flops, secs = misc.get_flops_and_seconds_per_device(state.model, batch["image"])
+      except Exception as e:  # pylint: disable=broad-except
+        logging.warning("Could not estimate the cost of a training step: %r", e)
+        flops = secs = None
+      train_cost_fn = make_train_cost_fn(flops, secs, mesh.world_size)
     if profile_hook is not None:
       profile_hook(step)
     _, metrics = step_fn(state, batch["image"], batch["labels"], train_loss_fn,
                          microsteps=microsteps, summarizer=summarizer)
-    progress_hook(step, scalar_metrics={"train": {k: v for k, v in metrics.items()
+    progress_hook(step, scalar_metrics={**train_cost_fn(step),
+                                        "train": {k: v for k, v in metrics.items()
                                                   if not isinstance(v, Mapping)}})
     if step % status_every == 0:
       check_device_status(state)

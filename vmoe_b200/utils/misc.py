@@ -163,3 +163,94 @@ def unflatten_dict(flat: Mapping[str, Any], sep: str = "/") -> Dict[str, Any]:
 def natural_sort_key(s: str):
   """Sort key under which ``a_2`` precedes ``a_11``."""
   return [int(t) if t.isdigit() else t for t in re.split(r"(\d+)", s)]
+
+
+def count_forward_flops(model: torch.nn.Module, *inputs) -> float:
+  """Matmul FLOPs (2 per multiply-add) of one forward pass on this device, counted from the
+  shapes seen by the model's linear layers, MLP blocks, expert MLPs, attention cores and
+  routers during one ``model(*inputs)`` call under ``no_grad``.
+
+  Expert MLPs are counted for the rows they actually process (experts x groups x capacity, or
+  slots for Soft MoE), not for the tokens that were routed. Elementwise work is not counted.
+  """
+  from vmoe_b200 import moe as moe_core
+  from vmoe_b200.models import vit_moe
+  total = [0.0]
+  handles = []
+
+  def rows_of(t: torch.Tensor) -> int:
+    return int(t.numel() // t.shape[-1])
+
+  def dense_hook(mod, args, out):
+    total[0] += 2.0 * rows_of(args[0]) * mod.weight.shape[0] * mod.weight.shape[1]
+
+  def mlp_hook(mod, args, out):
+    _, m, h = mod.w1.shape
+    total[0] += 2.0 * rows_of(args[0]) * (h * m + m * mod.w2.shape[1])
+
+  def attn_hook(mod, args, out):
+    q = args[0]
+    kv = args[1] if len(args) > 1 and args[1] is not None else q
+    b, tq, tk = q.shape[0], q.shape[1], kv.shape[1]
+    total[0] += 4.0 * b * mod.num_heads * tq * tk * mod.head_dim
+
+  def moe_hook(mod, args, out):
+    x = args[0]
+    tokens, hdim = rows_of(x), x.shape[-1]
+    groups = max(tokens // mod.group_size, 1)
+    e = mod.num_experts
+    router = mod.Router
+    rows = tokens
+    if hasattr(router, "num_selected_experts"):
+      kw = dict(getattr(router, "dispatcher_kwargs", {}) or {})
+      try:
+        cap = moe_core._resolve_capacity(
+            kw.get("capacity"), kw.get("capacity_factor"),
+            mod.group_size * router.num_selected_experts, e,
+            kw.get("capacity_ceil_or_round", "ceil"), kw.get("capacity_multiple_of", 4))
+        rows = groups * e * cap
+      except Exception:  # pylint: disable=broad-except
+        rows = tokens * router.num_selected_experts
+    elif getattr(router, "mu", None) is not None:
+      rows = groups * e * router.mu.shape[2]
+    _, m, h = mod.Mlp.w1.shape
+    total[0] += 2.0 * rows * 2 * h * m
+    dense = getattr(router, "dense", None)
+    if dense is not None:
+      total[0] += 2.0 * tokens * hdim * dense.weight.shape[0]
+    elif getattr(router, "mu", None) is not None:
+      total[0] += 2.0 * tokens * hdim * e * router.mu.shape[2] * 3  # logits, dispatch, combine
+
+  for mod in model.modules():
+    if isinstance(mod, vit_moe.MlpMoeBlock):
+      handles.append(mod.register_forward_hook(moe_hook))
+    elif isinstance(mod, vit_moe.MlpBlock):
+      handles.append(mod.register_forward_hook(mlp_hook))
+    elif isinstance(mod, vit_moe.MultiHeadDotProductAttention):
+      handles.append(mod.register_forward_hook(attn_hook))
+    elif isinstance(mod, vit_moe.Dense):
+      handles.append(mod.register_forward_hook(dense_hook))
+  was_training = model.training
+  try:
+    model.eval()
+    with torch.no_grad():
+      model(*inputs)
+  finally:
+    model.train(was_training)
+    for h in handles:
+      h.remove()
+  return total[0]
+
+
+def get_flops_and_seconds_per_device(model: torch.nn.Module, *inputs,
+                                     peak_flops_per_second: float = 1.418e15,
+                                     training: bool = True):
+  """``(flops, optimal_seconds)`` of one step on this device: three times the forward matmul
+  FLOPs when training (forward, activation gradients, weight gradients) and that count
+  divided by the sustained bf16 GEMM rate of the GPU (default: the rate measured with cuBLAS
+  on a B200 under its power cap). The reference reads both numbers from XLA's cost analysis
+  of the compiled step (``vmoe/utils.py:27-40``)."""
+  flops = count_forward_flops(model, *inputs) * (3.0 if training else 1.0)
+  if flops <= 0:
+    return None, None
+  return flops, flops / peak_flops_per_second
