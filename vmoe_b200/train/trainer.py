@@ -282,6 +282,52 @@ def check_device_status(state: TrainState) -> None:
     failure.check_status(comm.status, "expert exchange")
 
 
+def create_checkpoint_manager(*, workdir: str, every_steps: Optional[int] = None,
+                              keep_last: int = 1, keep_steps_multiple_of: Optional[int] = None,
+                              wait_seconds: Optional[int] = 300, mesh=None,
+                              **kwargs) -> "CheckpointManager":
+  """Factory with the reference's name (``vmoe/train/trainer.py:134-165``)."""
+  return CheckpointManager(workdir=workdir, every_steps=every_steps, keep_last=keep_last,
+                           keep_steps_multiple_of=keep_steps_multiple_of,
+                           wait_seconds=wait_seconds, mesh=mesh, **kwargs)
+
+
+def restore_or_create_train_state(*, ckpt_manager: "CheckpointManager", model_config,
+                                  optimizer_config, total_steps: int, mesh=None, device=None,
+                                  seed: int = 0, extra_rng_keys=(), initialization=None,
+                                  **model_overrides) -> TrainState:
+  """Creates the train state, then restores the latest checkpoint of ``ckpt_manager`` into it if
+  there is one; otherwise applies the optional fine-tuning ``initialization`` (kwargs of
+  ``initialize_train_state_from_checkpoint``). Mirrors ``vmoe/train/trainer.py:371-438``."""
+  state = create_train_state(model_config=model_config, optimizer_config=optimizer_config,
+                             total_steps=total_steps, mesh=mesh, device=device, seed=seed,
+                             extra_rng_keys=extra_rng_keys, **model_overrides)
+  if ckpt_manager.restore(state) is None and initialization:
+    initialize_train_state_from_checkpoint(state=state, mesh=mesh, **dict(initialization))
+  return state
+
+
+def accumulate_gradients_and_metrics(state: TrainState, images: Tensor, labels: Tensor,
+                                     loss_fn, microsteps: Optional[int] = None):
+  """Runs forward + backward over ``microsteps`` slices of the batch, leaving the summed
+  gradients in the parameters' ``.grad`` buffers (not yet reduced over ranks, not yet divided
+  by the number of slices: the optimizer does both); returns the averaged metrics
+  (``vmoe/train/trainer.py:76-131``)."""
+  state.model.train()
+  state.optimizer.zero_grad()
+  n = microsteps or 1
+  if n > 1 and images.shape[0] % n:
+    raise ValueError(f"batch {images.shape[0]} is not divisible by microsteps={n}")
+  metrics = None
+  for i in range(n):
+    total, m = compute_loss_and_metrics(state, images if n == 1 else images[i::n],
+                                        labels if n == 1 else labels[i::n], loss_fn)
+    total.backward()
+    m = _detach_tree(m)
+    metrics = m if metrics is None else _tree_add(metrics, m)
+  return _tree_scale(metrics, 1.0 / n) if n > 1 else metrics
+
+
 def make_train_cost_fn(flops_per_device: Optional[float], seconds_per_device: Optional[float],
                        num_devices: int = 1) -> Callable[[int], Dict[str, float]]:
   """Returns ``fn(step) -> {'flops': ..., 'device_seconds': ...}``: the total training cost up
