@@ -176,3 +176,21 @@ def test_config_dict():
   d = utils.ConfigDict({"x": ref, "y": ref})
   d.x = 4
   assert d.y == 4 and d.copy_and_resolve_references().to_dict() == {"x": 4, "y": 4}
+
+
+def test_hardware_and_logical_mesh_views():
+  import numpy as np
+  from vmoe_b200.parallel import mesh as mesh_lib
+  from vmoe_b200.parallel import partitioning
+  hw = partitioning.get_hardware_mesh(16, 8)
+  assert hw.shape == (8, 2) and hw[3, 1] == 11
+  lm = partitioning.get_logical_mesh(8, hw)     # 8 expert partitions, 2 replicas
+  assert lm.shape == (8, 2)
+  assert sorted(lm[:, 0]) == list(range(8))     # one expert group = the GPUs of node 0
+  assert partitioning.processes_have_contiguous_device_slices(lm, 8)
+  # Same assignment as the mesh every process builds for itself.
+  assert np.array_equal(lm, np.asarray(mesh_lib.mesh_layout(16, 8)))
+  lm4 = partitioning.get_logical_mesh(4, hw)    # two expert groups per node
+  assert np.array_equal(lm4, np.asarray(mesh_lib.mesh_layout(16, 4)))
+  x = object()
+  assert partitioning.with_sharding_constraint(x, ("expert",)) is x

@@ -89,3 +89,53 @@ def local_shard_slices(shape: Sequence[int], spec: PartitionSpec, mesh) -> Tuple
     step = n // parts
     out.append(slice(index * step, (index + 1) * step))
   return tuple(out)
+
+
+# ------------------------------------------------------------------ hardware / logical mesh views
+def get_hardware_mesh(world_size: int, local_world_size: int):
+  """The 2-D hardware mesh ``(device_on_process -> GPU of the node, process -> node)`` as an
+  array of global ranks: ``hw[d][n]`` is GPU ``d`` of node ``n`` (ranks are numbered node by
+  node, as torchrun does). Counterpart of ``get_hardware_mesh_other``
+  (``vmoe/partitioning.py:213-220``) with one process per GPU instead of one per host."""
+  import numpy as np
+  if world_size % local_world_size:
+    raise ValueError(f"{world_size} ranks do not fill nodes of {local_world_size} GPUs")
+  nodes = world_size // local_world_size
+  return np.arange(world_size).reshape(nodes, local_world_size).T
+
+
+def get_logical_mesh(num_partitions: int, hardware_mesh):
+  """``(expert, replica)`` array of ranks built from a hardware mesh: expert partitions are
+  filled with the GPUs of one node first (NVLink / NVSwitch neighbours) and spill over to
+  further nodes only when a node is too small, which is the reference's heuristic
+  (``vmoe/partitioning.py:136-151``: ``d = min(P, local)``, ``h = min(P // d, processes)``)."""
+  import numpy as np
+  hw = np.asarray(hardware_mesh)
+  local, nodes = hw.shape
+  world = local * nodes
+  if num_partitions < 1 or world % num_partitions:
+    raise ValueError(f"The hardware mesh with shape {hw.shape} cannot be automatically "
+                     f"partitioned into {num_partitions}.")
+  # Node-major order of ranks: consecutive ranks share a node.
+  order = hw.T.reshape(-1)
+  return order.reshape(world // num_partitions, num_partitions).T
+
+
+def processes_have_contiguous_device_slices(logical_mesh, local_world_size: int) -> bool:
+  """True if every node's ranks occupy a contiguous block of the logical mesh's columns or
+  rows (``vmoe/partitioning.py:93-114``); always true for the meshes built here."""
+  import numpy as np
+  lm = np.asarray(logical_mesh)
+  node = lm // local_world_size
+  for n in np.unique(node):
+    es, rs = np.nonzero(node == n)
+    if (es.max() - es.min() + 1) * (rs.max() - rs.min() + 1) != es.size:
+      return False
+  return True
+
+
+def with_sharding_constraint(x, partition_spec=None):
+  """Placement is explicit in this framework (each process owns its shard), so the GSPMD hint
+  of the reference (``vmoe/partitioning.py:424-429``) is the identity."""
+  del partition_spec
+  return x
