@@ -385,3 +385,29 @@ def sparse_moe_apply(expert_fn: Callable[..., Any], dispatcher: BaseDispatcher, 
   else:
     combined = dispatcher.combine(out)
   return (combined, aux) if has_aux else combined
+
+
+def sparse_moe_spmd(target: Callable[..., Any], variable_axes=None, split_rngs=None,
+                    has_aux: bool = False, methods=None):
+  """Reference-named lift (``vmoe/moe.py:388-448``): wraps a batched expert module / function
+  so that calling the result with ``(dispatcher, *inputs)`` dispatches every input, applies the
+  experts and combines the outputs.
+
+  ``variable_axes`` / ``split_rngs`` / ``methods`` configure Flax's vmap in the reference; here
+  the expert axis is the leading dimension of the module's parameters (each rank holds the
+  experts of its 'expert' mesh coordinate), so they are accepted and ignored.
+  """
+  del variable_axes, split_rngs, methods
+
+  def apply(dispatcher: BaseDispatcher, *inputs: Tensor):
+    return sparse_moe_apply(target, dispatcher, *inputs, has_aux=has_aux)
+
+  return apply
+
+
+def sparse_moe_spmd_with_axes(target: Callable[..., Any], variable_axes=None, partitioning_axis_names=None,
+                              split_rngs=None, has_aux: bool = False, methods=None):
+  """As ``sparse_moe_spmd``; the axis-name annotations of the reference
+  (``vmoe/moe.py:451-474``) have no counterpart because placement is explicit."""
+  del partitioning_axis_names
+  return sparse_moe_spmd(target, variable_axes, split_rngs, has_aux, methods)
