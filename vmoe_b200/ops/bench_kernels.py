@@ -4,6 +4,7 @@
 
 Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with residual),
 ``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
+``gemm_multi_dest`` (second expert GEMM storing row blocks into eight destination buffers),
 ``layernorm`` (forward and backward), ``attention`` (packed-QKV forward and backward),
 ``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward).
 Every case runs one warm-up pass, then times ``iters`` passes with CUDA events; inputs are
@@ -77,6 +78,29 @@ def gemm_dgrad(rows: int, iters: int):
     print(f"{name}: {us:.1f} us" + (f", {flops / us / 1e6:.0f} TFLOP/s" if "kernel" not in name else ""))
 
 
+def gemm_multi_dest(rows: int, iters: int):
+  """The second expert GEMM as the expert-parallel path runs it: (experts x rows, 3072) x
+  (3072, 768) with every block of rows / 8 output rows stored into its own destination buffer
+  (here all local; on several GPUs seven of the eight are peers' buffers), against the same
+  GEMM with one ordinary output."""
+  from vmoe_b200.ops import gemm as G
+  dev = "cuda"
+  dests = 8
+  block = (rows // dests) // 256 * 256
+  m = block * dests
+  hid = torch.randn(1, m, 3072, device=dev).bfloat16()
+  w2 = torch.randn(1, 768, 3072, device=dev).bfloat16()
+  b2 = torch.randn(1, 768, device=dev)
+  outs = [torch.empty(1, block, 768, device=dev, dtype=torch.bfloat16) for _ in range(dests)]
+  flops = 2 * m * 3072 * 768
+  for name, fn in {
+      "one output": lambda: G.gemm(hid, w2, bias=b2),
+      "eight destinations": lambda: G.gemm(hid, w2, bias=b2, out_multi=outs, mt_offset=block // 128),
+  }.items():
+    us = _timed(fn, iters)
+    print(f"{name}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+
+
 def layernorm(rows: int, iters: int):
   from vmoe_b200 import ops
   x = torch.randn(rows, 768, device="cuda").bfloat16().requires_grad_()
@@ -129,7 +153,7 @@ def router(rows: int, iters: int):
   print(f"router fwd: {_timed(fwd, iters):.1f} us; fwd+bwd: {_timed(both, iters):.1f} us")
 
 
-CASES = {"gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad, "layernorm": layernorm, "attention": attention,
+CASES = {"gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad, "gemm_multi_dest": gemm_multi_dest, "layernorm": layernorm, "attention": attention,
          "router": router}
 
 
