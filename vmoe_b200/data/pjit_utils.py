@@ -21,6 +21,10 @@ def _to_tensor(v: Any) -> torch.Tensor:
   return torch.from_numpy(np.ascontiguousarray(v))
 
 
+# Device buffers handed back by finished prefetchers, keyed by (device, name, shape, dtype).
+_SPARE_DEVICE_BUFFERS: Dict[Any, list] = {}
+
+
 class _PinnedPool:
   """Reusable pinned staging buffers keyed by (name, shape, dtype)."""
 
@@ -76,9 +80,32 @@ def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
     slots = ring.setdefault(key, [])
     i = cursor.get(key, 0)
     if len(slots) < nslots:
-      slots.append(torch.empty(t.shape, dtype=t.dtype, device=device))
+      # Buffers of finished prefetchers are reused, so a new pass over the data (the next
+      # epoch, an evaluation, a second measurement) does not go back to the allocator.
+      spare = _SPARE_DEVICE_BUFFERS.get((str(device),) + key)
+      if spare:
+        buf, last_use = spare.pop()
+        stream.wait_event(last_use)  # work of the previous owner that still reads the buffer
+      else:
+        buf = torch.empty(t.shape, dtype=t.dtype, device=device)
+      slots.append(buf)
     cursor[key] = (i + 1) % nslots
     return slots[i % len(slots)]
+
+  def release_ring():
+    # Hand the buffers to the next prefetcher, except those the consumer still holds (the last
+    # batch of a loop is often kept around). Work that reads them may still be queued: the
+    # next owner's copy stream waits for the event recorded here.
+    import sys
+    queue.clear()
+    done = torch.cuda.Event()
+    done.record(torch.cuda.current_stream(device))
+    for key, slots in ring.items():
+      while slots:
+        buf = slots.pop()
+        if sys.getrefcount(buf) <= 2:  # this frame's variable + getrefcount's argument
+          _SPARE_DEVICE_BUFFERS.setdefault((str(device),) + key, []).append((buf, done))
+    ring.clear()
 
   def enqueue(batch):
     out = {}
@@ -98,22 +125,28 @@ def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
       ev.record(stream)
     queue.append((out, ev))
 
-  it = iter(iterator)
-  exhausted = False
-  while True:
-    while not exhausted and len(queue) < max(1, size):
-      try:
-        enqueue(next(it))
-      except StopIteration:
-        exhausted = True
-    if not queue:
-      return
-    out, ev = queue.popleft()
-    torch.cuda.current_stream(device).wait_event(ev)
-    yield out
+  def _after_yield(out):
     done = torch.cuda.Event()
     done.record(torch.cuda.current_stream(device))
     for slots in ring.values():
       for t in slots:
         if any(t.data_ptr() == o.data_ptr() for o in out.values()):
           released[t.data_ptr()] = done
+
+  it = iter(iterator)
+  exhausted = False
+  try:
+    while True:
+      while not exhausted and len(queue) < max(1, size):
+        try:
+          enqueue(next(it))
+        except StopIteration:
+          exhausted = True
+      if not queue:
+        return
+      out, ev = queue.popleft()
+      torch.cuda.current_stream(device).wait_event(ev)
+      yield out
+      _after_yield(out)
+  finally:
+    release_ring()
