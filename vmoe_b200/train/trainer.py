@@ -7,6 +7,8 @@ Reference: ``vmoe/train/trainer.py`` — ``accumulate_gradients_and_metrics`` :7
 """
 from __future__ import annotations
 
+import contextlib
+
 import functools
 import logging
 import math
@@ -566,6 +568,20 @@ def _share_parameters(src: torch.nn.Module, dst: torch.nn.Module) -> None:
     p.requires_grad_(False)
 
 
+@contextlib.contextmanager
+def _step_annotation(name: str, step: int):
+  """NVTX range ``<name> <step>`` around a step (visible in Nsight / torch profiler traces); the
+  counterpart of ``jax.profiler.StepTraceAnnotation`` (``vmoe/train/trainer.py:822``)."""
+  on = torch.cuda.is_available()
+  if on:
+    torch.cuda.nvtx.range_push(f"{name} {step}")
+  try:
+    yield
+  finally:
+    if on:
+      torch.cuda.nvtx.range_pop()
+
+
 def create_progress_hook(*, writer, first_step, train_steps, **kwargs):
   from vmoe_b200.train import periodic_actions
   on_steps = set(kwargs.pop("on_steps", None) or []) | {first_step, train_steps}
@@ -702,10 +718,15 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
         logging.warning("Could not estimate the cost of a training step: %r", e)
         flops = secs = None
       train_cost_fn = make_train_cost_fn(flops, secs, mesh.world_size)
+      costs = {k: v for k, v in (("train/step_flops_per_device", flops),
+                                 ("train/step_seconds_per_device", secs)) if v is not None}
+      if costs:
+        writer.write_scalars(step, costs)
     if profile_hook is not None:
       profile_hook(step)
-    _, metrics = step_fn(state, batch["image"], batch["labels"], train_loss_fn,
-                         microsteps=microsteps, summarizer=summarizer)
+    with _step_annotation("train", step):
+      _, metrics = step_fn(state, batch["image"], batch["labels"], train_loss_fn,
+                           microsteps=microsteps, summarizer=summarizer)
     progress_hook(step, scalar_metrics={**train_cost_fn(step),
                                         "train": {k: v for k, v in metrics.items()
                                                   if not isinstance(v, Mapping)}})
