@@ -1,0 +1,68 @@
+"""Host-side failure detection logic against a fake key-value store (single process)."""
+import pytest
+import torch
+
+from vmoe_b200.parallel import failure
+
+
+class FakeStore:
+  def __init__(self):
+    self.d = {}
+
+  def set(self, k, v):
+    self.d[k] = v.encode() if isinstance(v, str) else v
+
+  def get(self, k):
+    return self.d[k]
+
+  def check(self, keys):
+    return all(k in self.d for k in keys)
+
+
+def test_heartbeat_passes_when_all_peers_reached_the_step():
+  store = FakeStore()
+  hbs = [failure.Heartbeat(store, rank=r, world_size=3) for r in range(3)]
+  for hb in hbs:
+    hb.beat(5)
+  hbs[0].check(5, timeout_s=0.1)
+  hbs[1].beat(6)
+  hbs[1].check(5, timeout_s=0.1)  # a peer that is ahead is fine
+
+
+def test_heartbeat_names_the_ranks_that_are_behind():
+  store = FakeStore()
+  hbs = [failure.Heartbeat(store, rank=r, world_size=3) for r in range(3)]
+  hbs[0].beat(2)
+  hbs[1].beat(2)
+  hbs[2].beat(1)
+  with pytest.raises(failure.PeerFailure) as e:
+    hbs[0].check(2, timeout_s=0.1, poll_s=0.01)
+  assert e.value.ranks == [2] and e.value.left == [] and e.value.step == 2
+
+
+def test_heartbeat_reports_a_peer_that_left_without_waiting_for_the_deadline():
+  store = FakeStore()
+  hbs = [failure.Heartbeat(store, rank=r, world_size=2) for r in range(2)]
+  hbs[0].beat(3)
+  hbs[1].beat(2)
+  hbs[1].leave()
+  with pytest.raises(failure.PeerFailure) as e:
+    hbs[0].check(3, timeout_s=30.0)
+  assert e.value.left == [1]
+
+
+def test_store_barrier_times_out_with_the_missing_ranks():
+  store = FakeStore()
+  failure.store_barrier("a", timeout_s=0.1, store=store, rank=0, world_size=1)
+  with pytest.raises(failure.BarrierTimeout) as e:
+    failure.store_barrier("b", timeout_s=0.05, store=store, rank=1, world_size=3, poll_s=0.01)
+  assert e.value.missing == [0, 2]
+
+
+def test_check_status_decodes_and_clears_the_word():
+  status = torch.tensor([8 | 32], dtype=torch.int32)
+  with pytest.raises(failure.DeviceWaitTimeout) as e:
+    failure.check_status(status, "expert exchange")
+  assert "ready-flag wait" in str(e.value) and "peer signal wait" in str(e.value)
+  assert int(status.item()) == 0
+  failure.check_status(status)  # zero: nothing to report
