@@ -385,3 +385,29 @@ def test_soft_router_fast_logits_match_reference_path():
   _close(w1, w2, 2e-2)
   _close(g1, x.grad, 5e-2)
   _close(gm1, r.mu.grad, 5e-2)
+
+
+def test_kernels_without_atomics_are_bitwise_reproducible():
+  """LayerNorm backward (fixed-order partial sums), the routing plan and a non-split GEMM give
+  identical bits when run twice on the same inputs."""
+  from vmoe_b200.ops import gemm as G
+  from vmoe_b200.ops import moe_ops
+  torch.manual_seed(0)
+  x = torch.randn(5000, 768, device=DEV).bfloat16().requires_grad_()
+  w = torch.randn(768, device=DEV).requires_grad_()
+  b = torch.randn(768, device=DEV).requires_grad_()
+  dy = torch.randn(5000, 768, device=DEV).bfloat16()
+  runs = []
+  for _ in range(2):
+    for t in (x, w, b):
+      t.grad = None
+    ops.layer_norm(x, w, b, 1e-6).backward(dy)
+    runs.append((x.grad.clone(), w.grad.clone(), b.grad.clone()))
+  for a, c in zip(*runs):
+    assert torch.equal(a, c)
+  gates = torch.softmax(torch.randn(4, 300, 8, device=DEV), -1)
+  plans = [moe_ops.routing_plan(gates, 2, 80, True) for _ in range(2)]
+  for a, c in zip(*plans):
+    assert torch.equal(a, c)
+  a_, b_ = torch.randn(700, 256, device=DEV).bfloat16(), torch.randn(520, 256, device=DEV).bfloat16()
+  assert torch.equal(G.gemm(a_, b_), G.gemm(a_, b_))
