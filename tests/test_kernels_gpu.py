@@ -411,3 +411,27 @@ def test_kernels_without_atomics_are_bitwise_reproducible():
     assert torch.equal(a, c)
   a_, b_ = torch.randn(700, 256, device=DEV).bfloat16(), torch.randn(520, 256, device=DEV).bfloat16()
   assert torch.equal(G.gemm(a_, b_), G.gemm(a_, b_))
+
+
+@pytest.mark.parametrize("has_cls", [True, False])
+def test_embed_finalize(has_cls):
+  from vmoe_b200.ops import elementwise
+  torch.manual_seed(0)
+  b, t, h = 5, 49, 64
+  emb = torch.randn(b, t, h, device=DEV).bfloat16().requires_grad_()
+  cls = torch.randn(1, 1, h, device=DEV).requires_grad_() if has_cls else None
+  pos = torch.randn(1, t + int(has_cls), h, device=DEV).requires_grad_()
+  out = elementwise.embed_finalize(emb, cls, pos)
+  probe = torch.randn_like(out)
+  out.backward(probe)
+  e2 = emb.detach().float().requires_grad_()
+  c2 = cls.detach().clone().requires_grad_() if has_cls else None
+  p2 = pos.detach().clone().requires_grad_()
+  ref = torch.cat([c2.expand(b, -1, -1), e2], dim=1) if has_cls else e2
+  ref = ref + p2
+  ref.backward(probe.float())
+  _close(out, ref, 1e-2)
+  _close(emb.grad, e2.grad, 1e-2)
+  _close(pos.grad, p2.grad, 1e-2)
+  if has_cls:
+    _close(cls.grad, c2.grad, 1e-2)

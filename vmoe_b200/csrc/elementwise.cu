@@ -679,6 +679,64 @@ extern "C" int vmoe_patchify(const void* img, int32_t img_is_bf16, void* out, in
   return launch_status("patchify");
 }
 
+// ------------------------------------------------------------------ embedding finalisation
+// out[b, 0, :] = cls + pos[0] (if a class token is used) and out[b, c + t, :] = emb[b, t, :] +
+// pos[c + t]: the class-token concatenation and the position-embedding add in one pass over
+// the patch embeddings. One warp per output row.
+__global__ void __launch_bounds__(256)
+embed_finalize_kernel(const __nv_bfloat16* __restrict__ emb, const float* __restrict__ cls,
+                      const float* __restrict__ pos, __nv_bfloat16* __restrict__ out,
+                      long long batch, int tokens, int h, int has_cls) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int out_tokens = tokens + has_cls;
+  const int chunks = h >> 3;
+  for (long long row = warp; row < batch * out_tokens; row += nwarps) {
+    const long long b = row / out_tokens;
+    const int t = static_cast<int>(row - b * out_tokens);
+    const bool is_cls = has_cls && t == 0;
+    const uint4* src = is_cls ? nullptr
+                              : reinterpret_cast<const uint4*>(
+                                    emb + (b * tokens + (t - has_cls)) * static_cast<long long>(h));
+    uint4* dst = reinterpret_cast<uint4*>(out + row * h);
+    for (int ch = lane; ch < chunks; ch += 32) {
+      float v[8];
+      if (is_cls) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = cls ? __ldg(cls + ch * 8 + i) : 0.f;
+      } else {
+        unpack8(__ldg(src + ch), v);
+      }
+      if (pos != nullptr) {
+        const float4 p0 = __ldg(reinterpret_cast<const float4*>(pos + static_cast<long long>(t) * h + ch * 8));
+        const float4 p1 = __ldg(reinterpret_cast<const float4*>(pos + static_cast<long long>(t) * h + ch * 8) + 1);
+        v[0] += p0.x; v[1] += p0.y; v[2] += p0.z; v[3] += p0.w;
+        v[4] += p1.x; v[5] += p1.y; v[6] += p1.z; v[7] += p1.w;
+      }
+      dst[ch] = pack8(v);
+    }
+  }
+}
+
+extern "C" int vmoe_embed_finalize(const void* emb, const float* cls, const float* pos, void* out,
+                                   int64_t batch, int64_t tokens, int64_t h, int has_cls,
+                                   vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (batch * (tokens + (has_cls ? 1 : 0)) == 0) return 0;
+  if (h % 8) {
+    set_error("%s (code %d)", "embed_finalize: hidden size must be a multiple of 8", 0);
+    return -1;
+  }
+  const long long rows = batch * (tokens + (has_cls ? 1 : 0));
+  const long long blocks = (rows * 32 + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
+  embed_finalize_kernel<<<grid, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(emb), cls, pos, static_cast<__nv_bfloat16*>(out), batch,
+      static_cast<int>(tokens), static_cast<int>(h), has_cls ? 1 : 0);
+  return launch_status("embed_finalize");
+}
+
 // ------------------------------------------------------------------ short rows inside packed tensors
 // LayerNorm over rows of h = 16 / 32 / 64 / 128 elements that are laid out as blocks of `inner`
 // consecutive rows, the blocks `*_outer` elements apart (e.g. the q slice of a packed

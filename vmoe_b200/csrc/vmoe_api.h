@@ -78,6 +78,13 @@ VMOE_API int vmoe_layernorm_bwd(const void* dy, const void* x, const float* gamm
                                 const float* mean, const float* rstd, const void* dres, void* dx,
                                 float* dgamma, float* dbeta, float* scratch, int64_t rows,
                                 int64_t h, vmoe_stream_t stream);
+// out (bf16 [batch][tokens + has_cls][h]) = concat(cls, emb) + pos: class token (fp32 [h], may
+// be NULL = zeros) in row 0 when has_cls, patch embeddings emb (bf16 [batch][tokens][h]) after
+// it, position embedding pos (fp32 [tokens + has_cls][h], may be NULL) added to every row.
+VMOE_API int vmoe_embed_finalize(const void* emb, const float* cls, const float* pos, void* out,
+                                 int64_t batch, int64_t tokens, int64_t h, int has_cls,
+                                 vmoe_stream_t stream);
+
 // LayerNorm over short rows (h = 16, 32, 64 or 128) that sit inside a larger tensor as blocks
 // of `inner` consecutive rows, the blocks `*_outer` elements apart: row r starts at
 // (r / inner) * outer + (r % inner) * h. Used on the q / k slices of a packed QKV projection.

@@ -525,7 +525,30 @@ class VisionTransformerMoe(nn.Module):
       return self.head(x)
     return x
 
+  def _fused_embed(self, images: Tensor) -> Optional[Tensor]:
+    """Patch embedding, class token and learned position embedding with the concat + add done
+    by one kernel; None when that path does not apply (then ``embed`` + the encoder's own
+    position embedding are used)."""
+    enc = self.Encoder
+    if not (images.is_cuda and self.dtype == torch.bfloat16 and ops.cuda_kernels_enabled()
+            and type(enc).forward is EncoderMoe.forward  # subclasses place pos-emb themselves
+            and self.classifier in ("token", "gap", "map", "0")
+            and enc.position_emb.get("name", "learned") == "learned"
+            and not (self.training and enc.dropout_rate > 0)):
+      return None
+    from vmoe_b200.ops import elementwise
+    x = self.embedding(self.patchify(images))
+    has_cls = self.classifier == "token"
+    pos = enc.posembed_input.pos_embedding
+    if x.shape[-1] % 8 or pos.shape[1] != x.shape[1] + int(has_cls):
+      return None
+    return elementwise.embed_finalize(x, self.cls if has_cls else None, pos)
+
   def forward(self, images: Tensor):
+    x = self._fused_embed(images)
+    if x is not None:
+      x, metrics = self.Encoder(x, add_pos=False)
+      return self.pool_and_head(x), metrics
     x = self.embed(images)
     x, metrics = self.Encoder(x)
     return self.pool_and_head(x), metrics
