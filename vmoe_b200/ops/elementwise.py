@@ -56,8 +56,8 @@ class _EmbedFinalizeFn(torch.autograd.Function):
     b, tt, h = dout.shape
     d_emb = dout[:, int(has_cls):] if ctx.needs_input_grad[0] else None
     d_cls = d_pos = None
-    if (cls_shape is not None and ctx.needs_input_grad[1]) or \\
-       (pos_shape is not None and ctx.needs_input_grad[2]):
+    if ((cls_shape is not None and ctx.needs_input_grad[1]) or
+        (pos_shape is not None and ctx.needs_input_grad[2])):
       total = reduce.colsum(dout.contiguous().reshape(b, tt * h)).reshape(tt, h)  # fp32
       if cls_shape is not None and ctx.needs_input_grad[1]:
         d_cls = total[0].reshape(cls_shape)
