@@ -46,6 +46,12 @@ def parse_args():
   ap.add_argument("--library-ops", action="store_true",
                   help="run PyTorch library ops instead of the package's kernels (stand-in baseline)")
   ap.add_argument("--skip-e2e", action="store_true")
+  ap.add_argument("--mode", default="train", choices=["train", "eval"],
+                  help="eval: forward-only evaluation steps (loss and precision sums) at capacity "
+                       "ratio 1.0, no optimizer")
+  ap.add_argument("--ensemble-size", type=int, default=1,
+                  help=">1: the ensemble-of-experts variant (inputs repeated per member, experts "
+                       "split into that many groups)")
   return ap.parse_args()
 
 
@@ -173,6 +179,12 @@ def main() -> int:
     cfg = common.get_vmoe_config(args.model, IMAGE_SIZE, NUM_CLASSES)
     cfg.encoder.dtype = "bfloat16"
     cfg.encoder.moe.router.dispatcher.batch_priority = True
+    if args.mode == "eval":
+      cfg.encoder.moe.router.dispatcher.capacity_factor = 1.0
+    if args.ensemble_size > 1:
+      cfg.name = "VisionTransformerMoeEnsemble"
+      cfg.encoder.moe.ensemble_size = args.ensemble_size
+      cfg.encoder.moe.group_size = cfg.encoder.moe.group_size * args.ensemble_size
   opt_cfg = dict(name="adam", b1=0.9, b2=0.999, weight_decay=0.1,
                  learning_rate=dict(schedule="warmup_linear_decay", peak_value=8e-4,
                                     end_value=1e-5, warmup_steps=10_000))
@@ -181,11 +193,24 @@ def main() -> int:
 
   import contextlib
   ctx = ops.use_cuda_kernels(False) if args.library_ops else contextlib.nullcontext()
+  loss_name, loss_kwargs = "sigmoid_xent", {}
+  if args.ensemble_size > 1:
+    loss_name, loss_kwargs = "ensemble_sigmoid_xent", {"ensemble_size": args.ensemble_size}
   with ctx:
-    state = trainer.create_train_state(model_config=cfg, optimizer_config=opt_cfg,
-                                       total_steps=total_steps, mesh=mesh, device=device,
-                                       seed=0, image_size=IMAGE_SIZE)
-    loss_fn, _, _ = trainer.get_loss_fn("sigmoid_xent")
+    if args.mode == "eval":
+      from vmoe_b200 import models as models_lib
+      from vmoe_b200.evaluate import evaluator
+      torch.manual_seed(0)
+      model = models_lib.create_model(cfg, deterministic=True, mesh=mesh,
+                                      image_size=IMAGE_SIZE).to(device)
+      model.eval()
+      state = None
+      _, loss_fn, pred_fn = trainer.get_loss_fn(loss_name, **loss_kwargs)
+    else:
+      state = trainer.create_train_state(model_config=cfg, optimizer_config=opt_cfg,
+                                         total_steps=total_steps, mesh=mesh, device=device,
+                                         seed=0, image_size=IMAGE_SIZE)
+      loss_fn, _, _ = trainer.get_loss_fn(loss_name, **loss_kwargs)
 
     gen = torch.Generator().manual_seed(1234 + rank)
     n_host_batches = 2
@@ -201,7 +226,13 @@ def main() -> int:
         dist.barrier()
       torch.cuda.synchronize()
 
+    ones = torch.ones(batch, device=device)
+
     def run_step(b):
+      if args.mode == "eval":
+        st = evaluator.evaluate_step(evaluator.EvalState.zeros(device), model, b["image"],
+                                     b["labels"], ones, loss_fn, pred_fn)
+        return (st.sum_loss / st.num).float()
       _, metrics = trainer.train_step(state, b["image"], b["labels"], loss_fn)
       return metrics["total_loss"]
 
@@ -257,8 +288,10 @@ def main() -> int:
   if rank == 0:
     value = batch * world / (ms_per_step / 1e3)
     out = {
-        "metric": ("V-MoE B/16 train images/s" if args.model == MODEL_DESC
-                   else f"{args.model} train images/s"),
+        "metric": ("V-MoE B/16 train images/s" if args.model == MODEL_DESC and args.mode == "train"
+                   and args.ensemble_size == 1 else
+                   f"{args.model}{' x' + str(args.ensemble_size) + ' ensemble' if args.ensemble_size > 1 else ''}"
+                   f" {args.mode} images/s"),
         "value": value,
         "unit": "images/s",
         "n_gpus": world,
@@ -273,7 +306,9 @@ def main() -> int:
         "impl": "library-ops stand-in" if args.library_ops else "vmoe_b200",
         "config": {
             "model": ("V-MoE B/16, 8 experts every odd block, K=2, capacity 1.05, BPR, sigmoid xent, Adam wd 0.1"
-                      if args.model == MODEL_DESC else args.model),
+                      if args.model == MODEL_DESC and args.mode == "train"
+                      and args.ensemble_size == 1 else
+                      f"{args.model}, mode={args.mode}, ensemble_size={args.ensemble_size}"),
             "global_batch": batch * world,
             "seq_len": 197,
             "parallelism": f"dp{world} x ep{num_partitions}",
