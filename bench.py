@@ -27,7 +27,6 @@ import os
 import statistics
 import subprocess
 import sys
-import time
 
 MODEL_DESC = "ViT-B/16, E=8, K=2, Every 2"
 NUM_CLASSES = 21843

@@ -13,7 +13,6 @@ import ast
 import importlib.util
 import logging
 import os
-import sys
 from typing import Any, Callable, List, Optional
 
 from vmoe_b200.parallel import mesh as mesh_lib

@@ -32,7 +32,7 @@ from vmoe_b200.checkpoints.types import (ArrayChunks, IndexInfo, LazyArrayChunks
                                          Slice, SliceNd)
 from vmoe_b200.parallel import mesh as mesh_lib
 from vmoe_b200.parallel import multihost_utils
-from vmoe_b200.parallel.partitioning import PartitionSpec, parse_partition_spec
+from vmoe_b200.parallel.partitioning import parse_partition_spec
 
 ThreadPool = base.ThreadPool
 MAX_CONCURRENT_BYTES = 8 * 1024 * 1024 * 1024

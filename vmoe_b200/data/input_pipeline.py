@@ -9,7 +9,6 @@ strings use the mini-language of ``pp_ops`` (reference: ``vmoe/data/input_pipeli
 """
 from __future__ import annotations
 
-import collections
 import logging
 import queue
 import threading

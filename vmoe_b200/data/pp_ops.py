@@ -12,7 +12,7 @@ tokenize, value_range (reference: ``vmoe/data/pp_ops.py:41-433``).
 from __future__ import annotations
 
 import io
-from typing import Any, Callable, Dict, Optional, Sequence
+from typing import Any, Dict
 
 import numpy as np
 import torch

@@ -10,7 +10,7 @@ mean rank across datasets (reference: ``vmoe/evaluate/fewshot.py:52-418``).
 from __future__ import annotations
 
 import time
-from typing import Any, Callable, Dict, Iterable, Mapping, Optional, Sequence, Tuple
+from typing import Any, Dict, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 import torch

@@ -7,7 +7,6 @@ reference's layout (reference: ``vmoe/nn/ensemble_routing.py:43-134``).
 """
 from __future__ import annotations
 
-from typing import Dict, Tuple
 
 import torch
 from torch import nn

@@ -3,12 +3,11 @@ Transformer (a V-MoE without MoE layers) and an MLP-Mixer (reference: ``vmoe/nn/
 wraps the ``vit_jax`` implementations)."""
 from __future__ import annotations
 
-from typing import Any, Mapping, Optional, Sequence
+from typing import Any, Mapping, Optional
 
 import torch
 from torch import nn
 
-from vmoe_b200 import ops
 from vmoe_b200.models import vit_moe
 
 

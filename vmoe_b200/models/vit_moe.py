@@ -13,7 +13,7 @@ Reference: ``vmoe/nn/vit_moe.py`` (MlpMoeBlock :48-124, MapHead :127-148, Encode
 from __future__ import annotations
 
 import math
-from typing import Any, Dict, Iterable, Mapping, Optional, Sequence, Tuple, Union
+from typing import Any, Dict, Iterable, Mapping, Optional, Sequence, Union
 
 import torch
 import torch.nn.functional as F

@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from vmoe_b200.ops import _lib, reduce
+from vmoe_b200.ops import reduce
 from vmoe_b200.ops.gemm import ACT_GELU, ACT_NONE, gemm
 
 _ENABLED = os.environ.get("VMOE_B200_KERNELS", "1") != "0"

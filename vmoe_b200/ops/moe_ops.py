@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from vmoe_b200 import moe as moe_core
-from vmoe_b200.ops import _lib, reduce
+from vmoe_b200.ops import _lib
 from vmoe_b200.ops.functional import _grad_target, bf16_shadow, bias_grad, wgrad
 from vmoe_b200.ops.gemm import ACT_GELU, gemm
 from vmoe_b200.parallel.exchange import ExpertExchange, LOCAL_EXCHANGE

@@ -9,7 +9,6 @@ the portable baseline; the fused GPU path pushes rows straight into peer memory 
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

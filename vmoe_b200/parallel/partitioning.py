@@ -8,7 +8,7 @@ tensors with at most one element are never partitioned (reference:
 from __future__ import annotations
 
 import re
-from typing import Any, Mapping, Optional, Sequence, Tuple, Union
+from typing import Any, Mapping, Sequence, Tuple
 
 import numpy as np
 

@@ -8,7 +8,7 @@ arrival is tracked with counters that live in the same buffers.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Sequence
 
 import torch
 

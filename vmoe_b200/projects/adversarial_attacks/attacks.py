@@ -9,7 +9,7 @@ and, per router, the intersection-over-union of the experts selected before and 
 from __future__ import annotations
 
 import dataclasses
-from typing import Any, Callable, Dict, Iterable, Mapping, Optional, Tuple
+from typing import Any, Callable, Dict, Iterable, Optional, Tuple
 
 import torch
 

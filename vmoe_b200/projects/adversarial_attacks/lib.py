@@ -13,7 +13,7 @@ import io
 import logging
 import math
 import os
-from typing import Any, Dict, Mapping, Optional
+from typing import Any, Mapping, Optional
 
 import numpy as np
 import torch

@@ -11,7 +11,7 @@ from __future__ import annotations
 import contextlib
 import functools
 import logging
-from typing import Any, Callable, Dict, Iterable, Mapping, Optional, Tuple
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
 
 import torch
 

@@ -7,7 +7,7 @@ recall@k in both directions, zero-shot embeds one prompt set per class.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Iterable, Mapping, Optional, Sequence
+from typing import Any, Dict, Iterable, Mapping, Sequence
 
 import torch
 

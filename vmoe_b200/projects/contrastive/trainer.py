@@ -6,8 +6,7 @@ value per image. Every rank contrasts its local images with its local texts (ref
 """
 from __future__ import annotations
 
-import logging
-from typing import Any, Callable, Dict, Mapping, Optional, Tuple
+from typing import Callable, Mapping, Optional
 
 import torch
 import torch.nn.functional as F

@@ -8,7 +8,6 @@ weights and bf16 payloads (reference: ``vmoe/projects/soft_moe/router.py:36-182`
 """
 from __future__ import annotations
 
-import logging
 from typing import Dict, Optional, Tuple
 
 import torch

@@ -13,8 +13,7 @@ the plan is then re-evaluated from the dual potentials so that gradients reach t
 """
 from __future__ import annotations
 
-import math
-from typing import Callable, Dict, Optional, Tuple
+from typing import Optional
 
 import torch
 

@@ -17,7 +17,6 @@ freeze. Regexes are searched in the Flax-style path of each parameter
 from __future__ import annotations
 
 import ctypes
-import math
 import re
 from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple, Union
 

@@ -7,7 +7,7 @@ from __future__ import annotations
 import contextlib
 import dataclasses
 import time
-from typing import Any, Callable, Dict, Iterable, Mapping, Optional
+from typing import Any, Callable, Dict, Iterable, Optional
 
 from vmoe_b200.utils.misc import flatten_dict
 

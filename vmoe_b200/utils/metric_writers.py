@@ -8,7 +8,7 @@ import contextlib
 import json
 import logging
 import os
-from typing import Any, Dict, List, Mapping, Optional
+from typing import Any, List, Mapping, Optional
 
 
 class MetricWriter:
