@@ -85,6 +85,44 @@ def main():
     dist.barrier()
     dist.destroy_process_group()
     return
+  if mode == "ckpt_fallback":
+    # Both ranks save steps 1 and 2; reading step 2 then fails on rank 1 only (a fake of the
+    # failing call), and both ranks must fall back to step 1 together.
+    from vmoe_b200.checkpoints import partitioned
+    make = lambda seed: trainer.create_train_state(
+        model_config=small_config(), optimizer_config=dict(name="adam", learning_rate=1e-3),
+        total_steps=10, mesh=mesh, seed=seed, image_size=64)
+    state = make(0)
+    mgr = trainer.CheckpointManager(workdir=outdir, every_steps=1, keep_last=5, mesh=mesh)
+    for step in (1, 2):
+      with torch.no_grad():
+        state.model.head.bias.fill_(float(step))
+      state.step = step
+      mgr.save(step, state, force=True)
+    mgr.wait_until_finished()
+    multihost_utils.sync_devices("saved")
+    real = partitioned.restore_checkpoint
+
+    def flaky(prefix, *args, **kwargs):
+      if rank == 1 and prefix.endswith("_2"):
+        raise OSError("injected read failure")
+      return real(prefix, *args, **kwargs)
+
+    partitioned.restore_checkpoint = flaky
+    fresh = make(1)
+    restored = mgr.restore(fresh)
+    result = {"restored": restored, "bias": float(fresh.model.head.bias.detach()[0]),
+              "step": fresh.step}
+    try:
+      mgr.restore(make(1), step=2)
+      result["explicit"] = "no error"
+    except trainer.CheckpointReadError as e:
+      result["explicit"] = str(e)
+    mgr.close()
+    json.dump(result, open(os.path.join(outdir, f"r{rank}.json"), "w"))
+    dist.barrier()
+    dist.destroy_process_group()
+    return
   multihost_utils.sync_devices("start")
   state = trainer.create_train_state(
       model_config=small_config(),

@@ -20,7 +20,7 @@ def test_two_tower_parameters_and_outputs():
                           image_size=size)
   names = {n.split(".")[0] for n, _ in model.named_parameters()}
   assert {"img", "txt", "s", "b"} <= names
-  assert model.s.item() == pytest.approx(math.log(2.0)) and model.b.item() == 1.0
+  assert model.s.detach().item() == pytest.approx(math.log(2.0)) and model.b.detach().item() == 1.0
   images = torch.zeros(batch, size, size, 3)
   texts = torch.zeros(batch, text_len, dtype=torch.int32)
   logits, _ = model(images, texts)

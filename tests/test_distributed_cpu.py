@@ -90,3 +90,11 @@ def test_heartbeat_reports_a_rank_that_leaves(tmp_path):
 def test_store_barrier_names_the_absent_rank(tmp_path):
   res = _launch(2, "barrier_absent", tmp_path)
   assert res[0]["result"] == "BarrierTimeout" and res[0]["missing"] == [1]
+
+
+def test_checkpoint_read_failure_on_one_rank_moves_all_ranks_to_the_previous_step(tmp_path):
+  r0, r1 = _launch(2, "ckpt_fallback", tmp_path)
+  for r in (r0, r1):
+    assert r["restored"] == 1 and r["step"] == 1 and r["bias"] == 1.0
+  assert "injected read failure" in r1["explicit"]
+  assert "on another rank" in r0["explicit"]

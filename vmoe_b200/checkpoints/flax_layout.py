@@ -109,7 +109,13 @@ def _to_flax_array(p: torch.Tensor, kind: str, extra) -> np.ndarray:
     out = t[0]
   else:
     raise ValueError(kind)
-  return to_numpy(out.contiguous())
+  out = out.contiguous()
+  if out.device.type == "cpu" and \
+      out.untyped_storage().data_ptr() == t.untyped_storage().data_ptr():
+    # A CPU parameter would be aliased by the NumPy array; checkpoints are written by
+    # background threads while training goes on, so take the snapshot now.
+    out = out.clone()
+  return to_numpy(out)
 
 
 def _from_flax_array(value: np.ndarray, p: torch.Tensor, kind: str, extra) -> torch.Tensor:

@@ -24,3 +24,16 @@ def sync_devices(name: str, main_process: int = 0, group=None) -> None:
   got = int(x.item())
   if got != h:
     raise ValueError(f"sync_devices failed for {name!r}. Found value: {got}, expected: {h}")
+
+
+def all_ranks_ok(ok: bool, group=None) -> bool:
+  """True if ``ok`` is true on every rank (a MIN all-reduce); the local value without a
+  process group. Lets all ranks take the same branch after a step that can fail on one of
+  them, e.g. reading a checkpoint shard."""
+  if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+    return bool(ok)
+  backend = dist.get_backend(group)
+  device = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else "cpu"
+  x = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+  dist.all_reduce(x, op=dist.ReduceOp.MIN, group=group)
+  return bool(int(x.item()))

@@ -356,6 +356,10 @@ def override_base_config(base, override):
 
 
 # ------------------------------------------------------------------------------------ checkpoints
+class CheckpointReadError(RuntimeError):
+  """A checkpoint that was asked for by step exists but cannot be read."""
+
+
 class CheckpointManager:
   """Train-state checkpoints ``<workdir>/ckpt/ckpt_<step>.{index,data-*}`` in the sharded
   format, saved asynchronously every ``every_steps`` steps; keeps the last ``keep_last``
@@ -434,16 +438,35 @@ class CheckpointManager:
     self._pool.join()
 
   def restore(self, state: TrainState, step: Optional[int] = None) -> Optional[int]:
+    """Restores ``step`` (raises if it cannot be read) or, without ``step``, the newest
+    checkpoint that every rank can read: a step whose files are truncated or corrupted is
+    reported and skipped, and the one before it is tried, so that a job restarted after a
+    crash in the middle of a save resumes from the last good step. Returns the restored step
+    or None."""
     from vmoe_b200.checkpoints import partitioned
-    step = self.latest_step() if step is None else step
-    if step is None:
-      return None
+    from vmoe_b200.parallel import multihost_utils
+    candidates = [step] if step is not None else sorted(self.all_steps(), reverse=True)
     _, specs = train_state_to_tree(state)
     specs["dataset_iterator"] = {"last_seen_index": None}
-    tree = partitioned.restore_checkpoint(f"{self.prefix}_{step}", shardings=specs,
-                                          mesh=self.mesh, thread_pool=self._pool)
-    load_train_state_from_tree(state, tree)
-    return step
+    for candidate in candidates:
+      tree, error = None, None
+      try:
+        tree = partitioned.restore_checkpoint(f"{self.prefix}_{candidate}", shardings=specs,
+                                              mesh=self.mesh, thread_pool=self._pool)
+      except Exception as e:  # pylint: disable=broad-except
+        error = e
+      if multihost_utils.all_ranks_ok(error is None):
+        load_train_state_from_tree(state, tree)
+        return candidate
+      if step is not None:
+        raise CheckpointReadError(
+            f"checkpoint {self.prefix}_{candidate} cannot be read"
+            + (f": {type(error).__name__}: {error}" if error is not None
+               else " on another rank")) from error
+      logging.error("Skipping checkpoint step %d (%s); trying the previous one.", candidate,
+                    f"{type(error).__name__}: {error}" if error is not None
+                    else "unreadable on another rank")
+    return None
 
 
 import numpy as np  # noqa: E402  (used by the checkpoint helpers below)
