@@ -387,6 +387,43 @@ def test_soft_router_fast_logits_match_reference_path():
   _close(gm1, r.mu.grad, 5e-2)
 
 
+@pytest.mark.parametrize("g, m, s", [(3, 196, 128), (2, 50, 24), (2, 7, 8), (1, 257, 96),
+                                     (5, 33, 1)])
+def test_soft_router_weights_kernel_matches_softmaxes(g, m, s):
+  from vmoe_b200.ops import router_ops
+  torch.manual_seed(0)
+  logits = (torch.randn(g, m, s, device=DEV) * 3).requires_grad_()
+  assert router_ops.soft_router_weights_supported(logits)
+  d1, c1 = router_ops.soft_router_weights(logits)
+  wd = torch.randn_like(d1)
+  wc = torch.randn_like(c1)
+  ((d1 * wd).sum() + (c1 * wc).sum()).backward()
+  g_both = logits.grad.clone()
+  logits.grad = None
+  d2 = torch.softmax(logits, dim=1)
+  c2 = torch.softmax(logits, dim=2)
+  ((d2 * wd).sum() + (c2 * wc).sum()).backward()
+  torch.testing.assert_close(d1, d2, rtol=1e-4, atol=1e-6)
+  torch.testing.assert_close(c1, c2, rtol=1e-4, atol=1e-6)
+  torch.testing.assert_close(g_both, logits.grad, rtol=1e-3, atol=1e-5)
+  # Only one of the two outputs used.
+  logits.grad = None
+  d3, _ = router_ops.soft_router_weights(logits)
+  (d3 * wd).sum().backward()
+  g_d = logits.grad.clone()
+  logits.grad = None
+  (torch.softmax(logits, dim=1) * wd).sum().backward()
+  torch.testing.assert_close(g_d, logits.grad, rtol=1e-3, atol=1e-5)
+  assert abs(d1.detach().sum(dim=1).mean().item() - 1.0) < 1e-4
+  assert abs(c1.detach().sum(dim=2).mean().item() - 1.0) < 1e-4
+
+
+def test_soft_router_weights_fall_back_for_groups_beyond_shared_memory():
+  from vmoe_b200.ops import router_ops
+  assert not router_ops.soft_router_weights_supported(torch.zeros(1, 600, 128, device=DEV))
+  assert not router_ops.soft_router_weights_supported(torch.zeros(1, 8, 8, device=DEV).half())
+
+
 def test_kernels_without_atomics_are_bitwise_reproducible():
   """LayerNorm backward (fixed-order partial sums), the routing plan and a non-split GEMM give
   identical bits when run twice on the same inputs."""

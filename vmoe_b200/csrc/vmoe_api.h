@@ -239,6 +239,18 @@ VMOE_API int vmoe_router_stats_bwd(const float* logits, const float* noise, cons
                                    int64_t group_size, int num_experts, float noise_std, int k,
                                    vmoe_stream_t stream);
 
+// Soft MoE routing weights of `groups` groups of m tokens x s slots (fp32, row-major per group):
+// dispatch = softmax over the tokens of each slot, combine = softmax over the slots of each
+// token. A group must fit in shared memory: m * s <= vmoe_soft_router_max_group_elements().
+VMOE_API int64_t vmoe_soft_router_max_group_elements(void);
+VMOE_API int vmoe_soft_router_fwd(const float* logits, float* dispatch, float* combine,
+                                  int64_t groups, int32_t m, int32_t s, vmoe_stream_t stream);
+// d_logits from the gradients of both weights (either may be NULL).
+VMOE_API int vmoe_soft_router_bwd(const float* dispatch, const float* combine,
+                                  const float* d_dispatch, const float* d_combine,
+                                  float* d_logits, int64_t groups, int32_t m, int32_t s,
+                                  vmoe_stream_t stream);
+
 // Last error text of the calling thread ("" if none).
 VMOE_API const char* vmoe_last_error(void);
 

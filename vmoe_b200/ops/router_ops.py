@@ -122,3 +122,57 @@ def router_stats(logits: torch.Tensor, noise: Optional[torch.Tensor], noise_std:
   loss is zero without noise and the GShard loss is computed on ``gates``.
   """
   return _RouterStatsFn.apply(logits, noise, float(noise_std), int(num_selected_experts))
+
+
+# ----------------------------------------------------------------------------- Soft MoE weights
+class _SoftRouterWeightsFn(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, logits):
+    g, m, s = logits.shape
+    logits = logits.contiguous()
+    dispatch = torch.empty_like(logits)
+    combine = torch.empty_like(logits)
+    rc = _lib.lib().vmoe_soft_router_fwd(
+        _vp(logits.data_ptr()), _vp(dispatch.data_ptr()), _vp(combine.data_ptr()),
+        ctypes.c_int64(g), ctypes.c_int32(m), ctypes.c_int32(s), _vp(_lib.stream_ptr()))
+    _lib.check(rc, "vmoe_soft_router_fwd")
+    _lib.count_launch()
+    ctx.save_for_backward(dispatch, combine)
+    return dispatch, combine
+
+  @staticmethod
+  def backward(ctx, d_dispatch, d_combine):
+    dispatch, combine = ctx.saved_tensors
+    g, m, s = dispatch.shape
+    if d_dispatch is None and d_combine is None:
+      return None
+    if d_dispatch is not None:
+      d_dispatch = d_dispatch.contiguous().float()
+    if d_combine is not None:
+      d_combine = d_combine.contiguous().float()
+    d_logits = torch.empty_like(dispatch)
+    rc = _lib.lib().vmoe_soft_router_bwd(
+        _vp(dispatch.data_ptr()), _vp(combine.data_ptr()), _vp(_lib.ptr(d_dispatch)),
+        _vp(_lib.ptr(d_combine)), _vp(d_logits.data_ptr()), ctypes.c_int64(g),
+        ctypes.c_int32(m), ctypes.c_int32(s), _vp(_lib.stream_ptr()))
+    _lib.check(rc, "vmoe_soft_router_bwd")
+    _lib.count_launch()
+    return d_logits
+
+
+def soft_router_weights_supported(logits: torch.Tensor) -> bool:
+  if not (logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 3 and
+          fn.cuda_kernels_enabled()):
+    return False
+  _, m, s = logits.shape
+  limit = _lib.lib().vmoe_soft_router_max_group_elements
+  limit.restype = ctypes.c_int64
+  return 0 < m <= 4096 and 0 < s <= 4096 and m * s <= int(limit())
+
+
+def soft_router_weights(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+  """``logits (G, tokens, slots)`` fp32 -> ``(dispatch, combine)``: softmax over the tokens
+  (axis 1) and softmax over the slots (axis 2), computed by one kernel per direction of the
+  autograd graph (reference formulation: ``vmoe/projects/soft_moe/router.py:94-96``)."""
+  return _SoftRouterWeightsFn.apply(logits)

@@ -100,9 +100,16 @@ class SoftRouter(nn.Module):
       logits = torch.einsum("gmd,dnp->gmnp", x, mu)
     if not self.is_deterministic() and self.noise_std > 0:
       logits = logits + self.noise_std * torch.randn_like(logits)
-    dispatch_weights = torch.softmax(logits, dim=1)
     g, m, n, p = logits.shape
-    combine_weights = torch.softmax(logits.reshape(g, m, n * p), dim=-1).reshape(g, m, n, p)
+    from vmoe_b200.ops import router_ops
+    flat = logits.reshape(g, m, n * p)
+    if router_ops.soft_router_weights_supported(flat):
+      dispatch_weights, combine_weights = router_ops.soft_router_weights(flat)
+      dispatch_weights = dispatch_weights.reshape(g, m, n, p)
+      combine_weights = combine_weights.reshape(g, m, n, p)
+    else:
+      dispatch_weights = torch.softmax(logits, dim=1)
+      combine_weights = torch.softmax(flat, dim=-1).reshape(g, m, n, p)
     dispatcher = moe.Bfloat16Dispatcher(moe.EinsumDispatcher(
         combine_weights=combine_weights, dispatch_weights=dispatch_weights,
         exchange=self.exchange))
