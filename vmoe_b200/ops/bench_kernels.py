@@ -6,7 +6,8 @@ Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with r
 ``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
 ``gemm_multi_dest`` (second expert GEMM storing row blocks into eight destination buffers),
 ``layernorm`` (forward and backward), ``attention`` (packed-QKV forward and backward),
-``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward).
+``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward),
+``soft_router`` (Soft MoE dispatch / combine softmaxes, forward and backward).
 Every case runs one warm-up pass, then times ``iters`` passes with CUDA events; inputs are
 larger than the L2 cache. The same commands are the workloads of the profiler summaries kept
 under ``profiles/``.
@@ -153,7 +154,30 @@ def router(rows: int, iters: int):
   print(f"router fwd: {_timed(fwd, iters):.1f} us; fwd+bwd: {_timed(both, iters):.1f} us")
 
 
-CASES = {"gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad, "gemm_multi_dest": gemm_multi_dest, "layernorm": layernorm, "attention": attention,
+def soft_router(rows: int, iters: int):
+  """Soft MoE routing weights of ``rows // 196`` groups of 196 tokens x 128 slots: both
+  softmaxes in one kernel, and the fused backward, against the two PyTorch softmaxes."""
+  from vmoe_b200.ops import router_ops
+  groups = max(rows // 196, 1)
+  logits = (torch.randn(groups, 196, 128, device="cuda") * 3).requires_grad_()
+  d, c = router_ops.soft_router_weights(logits)
+  gd, gc = torch.randn_like(d), torch.randn_like(c)
+  nbytes = logits.numel() * 4
+  us_f = _timed(lambda: router_ops.soft_router_weights(logits), iters)
+  us_b = _timed(lambda: torch.autograd.grad([d, c], logits, [gd, gc], retain_graph=True), iters)
+
+  def torch_fwd():
+    return torch.softmax(logits, dim=1), torch.softmax(logits, dim=2)
+
+  d2, c2 = torch_fwd()
+  us_tf = _timed(torch_fwd, iters)
+  us_tb = _timed(lambda: torch.autograd.grad([d2, c2], logits, [gd, gc], retain_graph=True), iters)
+  print(f"soft router weights fwd: {us_f:.1f} us ({3 * nbytes / us_f / 1e3:.0f} GB/s; PyTorch "
+        f"{us_tf:.1f} us); bwd: {us_b:.1f} us ({5 * nbytes / us_b / 1e3:.0f} GB/s; PyTorch "
+        f"{us_tb:.1f} us)")
+
+
+CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad, "gemm_multi_dest": gemm_multi_dest, "layernorm": layernorm, "attention": attention,
          "router": router}
 
 
