@@ -45,3 +45,30 @@ def test_train_main_with_config_file_and_overrides(tmp_path):
   files = os.listdir(workdir / "ckpt")
   assert any(f.startswith("ckpt_2.index") for f in files), files  # the override took effect
   assert "val/prec@1" in res.stderr or "val/prec@1" in res.stdout
+
+
+def test_bench_reference_arm_prints_one_json_line():
+  import json
+  import subprocess
+  import sys
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference",
+                        "--gpus", "1", "--steps", "2", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=300, cwd=root)
+  assert out.returncode == 0, out.stderr[-2000:]
+  lines = [l for l in out.stdout.splitlines() if l.strip()]
+  assert len(lines) == 1
+  record = json.loads(lines[0])
+  assert record["impl"] == "reference"
+  assert "unavailable" in record and "\n" not in record["unavailable"]
+
+
+def test_bench_help_lists_the_contract_flags():
+  import subprocess
+  import sys
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--help"],
+                       capture_output=True, text=True, timeout=120, cwd=root)
+  assert out.returncode == 0
+  for flag in ("--gpus", "--steps", "--warmup", "--impl", "--mode", "--ensemble-size"):
+    assert flag in out.stdout
