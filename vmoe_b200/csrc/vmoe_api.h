@@ -251,6 +251,15 @@ VMOE_API int vmoe_soft_router_bwd(const float* dispatch, const float* combine,
                                   float* d_logits, int64_t groups, int32_t m, int32_t s,
                                   vmoe_stream_t stream);
 
+// Host-side batch assembly (no device work, no state): dst[i] = srcs[i] for n blocks of
+// bytes_each bytes, or dst[i][j] = srcs[i][j] * scale + shift from uint8 to float32, spread over
+// `threads` threads (0 = one per core, at most 64). Has no counterpart in the reference, whose
+// batches are assembled by tf.data.
+VMOE_API int vmoe_collate_rows(const void* const* srcs, int64_t n, int64_t bytes_each, void* dst,
+                               int32_t threads);
+VMOE_API int vmoe_collate_u8_to_f32(const uint8_t* const* srcs, int64_t n, int64_t elems_each,
+                                    float* dst, float scale, float shift, int32_t threads);
+
 // Last error text of the calling thread ("" if none).
 VMOE_API const char* vmoe_last_error(void);
 

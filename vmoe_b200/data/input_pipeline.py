@@ -52,8 +52,11 @@ def _to_numpy(v):
 
 
 def _stack(examples) -> Dict[str, np.ndarray]:
+  """One batch from a list of examples; large fields are copied by the multi-threaded host
+  collate (``vmoe_b200/data/native.py``)."""
+  from vmoe_b200.data import native
   keys = examples[0].keys()
-  return {k: np.stack([_to_numpy(e[k]) for e in examples]) for k in keys}
+  return {k: native.stack([_to_numpy(e[k]) for e in examples]) for k in keys}
 
 
 class DatasetIterator:
