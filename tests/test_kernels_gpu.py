@@ -424,6 +424,27 @@ def test_soft_router_weights_fall_back_for_groups_beyond_shared_memory():
   assert not router_ops.soft_router_weights_supported(torch.zeros(1, 8, 8, device=DEV).half())
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("xshape, shape, roll_axis", [
+    ((1, 6, 5, 3), (1, 6, 2), 1), ((1, 8, 7), (1, 1, 3), 1), ((6,), (6, 2), 0),
+    ((2, 4, 33), (2, 4, 4), 1), ((16, 224, 224, 3), (1, 2), 0)])
+def test_mixup_kernel_matches_rolled_sums(dtype, xshape, shape, roll_axis):
+  from vmoe_b200.train import trainer
+  torch.manual_seed(0)
+  x = torch.randn(*xshape, device=DEV).to(dtype)
+  y = torch.rand(*xshape[:len(shape) - 1], 5, device=DEV)
+  got = trainer.mixup(torch.Generator().manual_seed(3), (x, y), concentration=0.5, shape=shape,
+                      roll_axis=roll_axis)
+  with ops.use_cuda_kernels(False):
+    want = trainer.mixup(torch.Generator().manual_seed(3), (x, y), concentration=0.5,
+                         shape=shape, roll_axis=roll_axis)
+  tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+  for a, b in zip(got, want):
+    assert a.shape == b.shape and a.dtype == b.dtype
+    torch.testing.assert_close(a.float(), b.float(), rtol=tol, atol=tol)
+  assert not torch.equal(got[0], x)
+
+
 def test_kernels_without_atomics_are_bitwise_reproducible():
   """LayerNorm backward (fixed-order partial sums), the routing plan and a non-split GEMM give
   identical bits when run twice on the same inputs."""

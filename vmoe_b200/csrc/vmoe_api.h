@@ -251,6 +251,12 @@ VMOE_API int vmoe_soft_router_bwd(const float* dispatch, const float* combine,
                                   float* d_logits, int64_t groups, int32_t m, int32_t s,
                                   vmoe_stream_t stream);
 
+// Mixup: x and out viewed as (lead, batch, inner), fp32 or bf16; weights fp32 (size, lead, batch);
+// out[l, b, :] = sum_i weights[i, l, b] * x[l, (b + i) % batch, :], size <= 8.
+VMOE_API int vmoe_mixup(const void* x, void* out, const float* weights, int32_t is_bf16,
+                        int64_t lead, int64_t batch, int64_t inner, int32_t size,
+                        vmoe_stream_t stream);
+
 // Host-side batch assembly (no device work, no state): dst[i] = srcs[i] for n blocks of
 // bytes_each bytes, or dst[i][j] = srcs[i][j] * scale + shift from uint8 to float32, spread over
 // `threads` threads (0 = one per core, at most 64). Has no counterpart in the reference, whose

@@ -70,3 +70,30 @@ def embed_finalize(emb: torch.Tensor, cls, pos) -> torch.Tensor:
   """``emb (B, T, H)`` bf16; ``cls (1, 1, H)`` fp32 or None; ``pos (1, T + has_cls, H)`` fp32 or
   None. Returns ``(B, T + has_cls, H)`` bf16."""
   return _EmbedFinalizeFn.apply(emb, cls, pos)
+
+
+def mixup_supported(x: torch.Tensor, size: int) -> bool:
+  from vmoe_b200.ops import functional
+  return (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and 1 <= size <= 8 and
+          x.numel() > 0 and functional.cuda_kernels_enabled())
+
+
+def mixup_rows(x: torch.Tensor, weights: torch.Tensor, roll_axis: int) -> torch.Tensor:
+  """``sum_i weights[i] * roll(x, -i, roll_axis)`` in one kernel. ``weights`` has shape
+  ``(size,) + x.shape[:roll_axis + 1]`` (already broadcast over the leading dims); no gradient."""
+  x = x.contiguous()
+  size = weights.shape[0]
+  lead = 1
+  for d in x.shape[:roll_axis]:
+    lead *= d
+  batch = x.shape[roll_axis]
+  inner = x.numel() // (lead * batch)
+  w = weights.to(device=x.device, dtype=torch.float32).reshape(size, lead * batch).contiguous()
+  out = torch.empty_like(x)
+  rc = _lib.lib().vmoe_mixup(
+      _vp(x.data_ptr()), _vp(out.data_ptr()), _vp(w.data_ptr()),
+      ctypes.c_int32(int(x.dtype == torch.bfloat16)), ctypes.c_int64(lead), ctypes.c_int64(batch),
+      ctypes.c_int64(inner), ctypes.c_int32(size), _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_mixup")
+  _lib.count_launch()
+  return out

@@ -207,6 +207,13 @@ def mixup(generator: Optional[torch.Generator], tree, *, concentration: float,
   alpha = torch.sort(alpha, dim=-1, descending=True).values
   alpha = torch.movedim(alpha, -1, 0)  # (size, *batch dims)
   def mix(x):
+    from vmoe_b200.ops import elementwise
+    if (roll_axis == batch_ndim - 1 and not x.requires_grad and
+        elementwise.mixup_supported(x, shape[-1])):
+      # One kernel instead of `size` rolled copies: the weights depend only on the dims up to
+      # and including the rolled one.
+      full = alpha.expand((alpha.shape[0],) + tuple(x.shape[:batch_ndim])).contiguous()
+      return elementwise.mixup_rows(x, full, roll_axis)
     a = alpha.to(device=x.device, dtype=x.dtype if x.is_floating_point() else torch.float32)
     a = a.reshape(tuple(a.shape) + (1,) * (x.dim() - batch_ndim))
     return sum(a[i] * torch.roll(x, -i, dims=roll_axis) for i in range(shape[-1]))
