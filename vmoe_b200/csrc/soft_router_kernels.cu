@@ -35,10 +35,13 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // smem: tile[m * s] | row_max[m] | row_inv[m] | col_max[s] | col_inv[s]
+// VEC4: s is a multiple of 4 and all three arrays are 16-byte aligned, so the tile is moved with
+// 16-byte accesses.
+template <bool VEC4>
 __global__ void __launch_bounds__(kSoftThreads)
 soft_router_fwd_kernel(const float* __restrict__ logits, float* __restrict__ dispatch,
                        float* __restrict__ combine, int m, int s) {
-  extern __shared__ float soft_smem[];
+  extern __shared__ __align__(16) float soft_smem[];
   float* tile = soft_smem;
   float* row_max = tile + static_cast<size_t>(m) * s;
   float* row_inv = row_max + m;
@@ -48,19 +51,44 @@ soft_router_fwd_kernel(const float* __restrict__ logits, float* __restrict__ dis
   const int total = m * s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  for (int i = threadIdx.x; i < total; i += kSoftThreads) tile[i] = logits[base + i];
+  if (VEC4) {
+    const float4* src = reinterpret_cast<const float4*>(logits + base);
+    float4* dst = reinterpret_cast<float4*>(tile);
+    for (int i = threadIdx.x; i < total / 4; i += kSoftThreads) dst[i] = src[i];
+  } else {
+    for (int i = threadIdx.x; i < total; i += kSoftThreads) tile[i] = logits[base + i];
+  }
   __syncthreads();
 
-  // Rows: one warp per token, lanes stride over the slots.
-  for (int r = warp; r < m; r += kSoftWarps) {
-    const float* row = tile + static_cast<size_t>(r) * s;
+  // Rows: eight lanes per token, four tokens per warp at a time (the trip count is the same
+  // for all lanes, so the shuffles below always run with a full warp).
+  const int sub = lane >> 3, sl = lane & 7;
+  for (int r0 = warp * 4; r0 < m; r0 += kSoftWarps * 4) {
+    const int r = r0 + sub;
+    const bool valid = r < m;
+    const float* row = tile + static_cast<size_t>(valid ? r : 0) * s;
+    // The four tokens of a warp start at different 8-column blocks, so that with a row
+    // length that is a multiple of 32 words they read different shared-memory banks.
+    const int nblk = s >> 3, tail = nblk << 3;
     float mx = -INFINITY;
-    for (int c = lane; c < s; c += 32) mx = fmaxf(mx, row[c]);
-    mx = warp_max(mx);
+    if (valid) {
+      for (int k = 0, blk = sub % max(nblk, 1); k < nblk; ++k, blk = blk + 1 == nblk ? 0 : blk + 1)
+        mx = fmaxf(mx, row[(blk << 3) + sl]);
+      if (tail + sl < s) mx = fmaxf(mx, row[tail + sl]);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     float sum = 0.f;
-    for (int c = lane; c < s; c += 32) sum += __expf(row[c] - mx);
-    sum = warp_sum(sum);
-    if (lane == 0) {
+    if (valid) {
+      for (int k = 0, blk = sub % max(nblk, 1); k < nblk; ++k, blk = blk + 1 == nblk ? 0 : blk + 1)
+        sum += __expf(row[(blk << 3) + sl] - mx);
+      if (tail + sl < s) sum += __expf(row[tail + sl] - mx);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (valid && sl == 0) {
       row_max[r] = mx;
       row_inv[r] = 1.f / sum;
     }
@@ -76,11 +104,33 @@ soft_router_fwd_kernel(const float* __restrict__ logits, float* __restrict__ dis
   }
   __syncthreads();
 
-  for (int i = threadIdx.x; i < total; i += kSoftThreads) {
-    const int r = i / s, c = i - r * s;
-    const float x = tile[i];
-    dispatch[base + i] = __expf(x - col_max[c]) * col_inv[c];
-    combine[base + i] = __expf(x - row_max[r]) * row_inv[r];
+  // Outputs: one warp per token row, lanes across the slots.
+  for (int r = warp; r < m; r += kSoftWarps) {
+    const float rmx = row_max[r], rinv = row_inv[r];
+    const long long rbase = base + static_cast<long long>(r) * s;
+    const float* row = tile + static_cast<size_t>(r) * s;
+    if (VEC4) {
+      for (int c = lane * 4; c < s; c += 128) {
+        const float4 x = *reinterpret_cast<const float4*>(row + c);
+        float4 d, o;
+        d.x = __expf(x.x - col_max[c + 0]) * col_inv[c + 0];
+        d.y = __expf(x.y - col_max[c + 1]) * col_inv[c + 1];
+        d.z = __expf(x.z - col_max[c + 2]) * col_inv[c + 2];
+        d.w = __expf(x.w - col_max[c + 3]) * col_inv[c + 3];
+        o.x = __expf(x.x - rmx) * rinv;
+        o.y = __expf(x.y - rmx) * rinv;
+        o.z = __expf(x.z - rmx) * rinv;
+        o.w = __expf(x.w - rmx) * rinv;
+        *reinterpret_cast<float4*>(dispatch + rbase + c) = d;
+        *reinterpret_cast<float4*>(combine + rbase + c) = o;
+      }
+    } else {
+      for (int c = lane; c < s; c += 32) {
+        const float x = row[c];
+        dispatch[rbase + c] = __expf(x - col_max[c]) * col_inv[c];
+        combine[rbase + c] = __expf(x - rmx) * rinv;
+      }
+    }
   }
 }
 
@@ -160,19 +210,28 @@ extern "C" int vmoe_soft_router_fwd(const float* logits, float* dispatch, float*
     set_error("%s (code %d)", "soft router: a group does not fit in shared memory", m);
     return -1;
   }
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(soft_router_fwd_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+  const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec4 = s % 4 == 0 && aligned(logits) && aligned(dispatch) && aligned(combine);
+  static size_t configured[2] = {0, 0};
+  if (smem > 48 * 1024 && smem > configured[vec4]) {
+    cudaError_t e = vec4 ? cudaFuncSetAttribute(soft_router_fwd_kernel<true>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(smem))
+                         : cudaFuncSetAttribute(soft_router_fwd_kernel<false>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(smem));
     if (e != cudaSuccess) {
       set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
       return -5;
     }
-    configured = smem;
+    configured[vec4] = smem;
   }
-  soft_router_fwd_kernel<<<static_cast<unsigned>(groups), kSoftThreads, smem, stream>>>(
-      logits, dispatch, combine, m, s);
+  if (vec4)
+    soft_router_fwd_kernel<true><<<static_cast<unsigned>(groups), kSoftThreads, smem, stream>>>(
+        logits, dispatch, combine, m, s);
+  else
+    soft_router_fwd_kernel<false><<<static_cast<unsigned>(groups), kSoftThreads, smem, stream>>>(
+        logits, dispatch, combine, m, s);
   return check_launch();
 }
 
