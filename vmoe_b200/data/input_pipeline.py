@@ -220,6 +220,9 @@ def get_dataset(*, variant: str, name: str, split: str, batch_size: int, process
 def get_datasets(config: Mapping[str, Any]) -> Dict[str, DatasetIterator]:
   datasets = {}
   for variant, variant_config in config.items():
+    if not (hasattr(variant_config, "to_dict") or isinstance(variant_config, Mapping)):
+      raise TypeError(f"The config for the {variant!r} variant is not a dict but "
+                      f"{type(variant_config)}: {variant_config!r}")
     kwargs = variant_config.to_dict() if hasattr(variant_config, "to_dict") else dict(variant_config)
     datasets[variant] = get_dataset(variant=variant, **kwargs)
   return datasets
