@@ -6,6 +6,7 @@
 // LayerNorm; :337-339 patch-embedding conv input).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <stdint.h>
 
 #include "ptx_sm100.cuh"
@@ -818,7 +819,9 @@ constexpr int kLnStaticMaxCtas = 148 * 3;     // grid cap of the backward kernel
 constexpr int kLnStaticMaxHidden = 1024;
 constexpr int kLnStaticMaxDevices = 64;
 static __device__ __align__(256) float g_ln_bwd_scratch[kLnStaticMaxCtas * 2 * kLnStaticMaxHidden];
-float* g_ln_bwd_scratch_ptr[kLnStaticMaxDevices] = {};
+// Per-device cache of the array's device address; atomic so that threads racing through the
+// first call on a device publish and read the (identical) value safely.
+std::atomic<float*> g_ln_bwd_scratch_ptr[kLnStaticMaxDevices];
 }  // namespace
 
 extern "C" int vmoe_layernorm_bwd_static(const void* dy, const void* x, const float* gamma,
@@ -842,17 +845,16 @@ extern "C" int vmoe_layernorm_bwd_static(const void* dy, const void* x, const fl
               static_cast<int>(e));
     return -5;
   }
-  if (g_ln_bwd_scratch_ptr[dev] == nullptr) {
+  float* ptr = g_ln_bwd_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     // One-time set-up per device: resolve the device address of the static array.
-    float* ptr = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_ln_bwd_scratch);
     if (e != cudaSuccess || ptr == nullptr) {
       set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
       return -5;
     }
-    g_ln_bwd_scratch_ptr[dev] = ptr;
+    g_ln_bwd_scratch_ptr[dev].store(ptr, std::memory_order_release);
   }
-  return layernorm_bwd_launch(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta,
-                              g_ln_bwd_scratch_ptr[dev], rows, h,
+  return layernorm_bwd_launch(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, ptr, rows, h,
                               static_cast<cudaStream_t>(stream_));
 }

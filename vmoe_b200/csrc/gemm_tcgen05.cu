@@ -25,6 +25,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include "moe_push.cuh"
 #include "ptx_sm100.cuh"
 #include "tma_host.h"
 #include "vmoe_api.h"
@@ -42,13 +43,28 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;    // one 64 x 64 MN-major box = 8 KiB
 constexpr int TMEM_COLS = 512;              // two 128 x 256 fp32 accumulators
 constexpr int EPI_WARPS = 8;                // two per TMEM lane quadrant, 128 columns each
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
-constexpr int EPI_CHUNK_BYTES = 32 * 32 * 2;  // 32 rows x 32 bf16 columns, 64 B swizzled rows
-constexpr int EPI_STAGE_BYTES = EPI_WARPS * 2 * EPI_CHUNK_BYTES;  // C and C2 staging per warp
+constexpr int EPI_CHUNK_BYTES = 32 * 32 * 2;  // 32 rows x 32 bf16 columns
+// Staging per epilogue warp: two 32 x 32 tiles (64 B swizzled rows) for C and the second output /
+// epilogue input. (Measured: 32 x 64 tiles with 128-byte rows for every output, paid for with one
+// pipeline stage less in pair mode, did not make the K = 768 GEMMs faster and cost the long-K
+// ones 5 %; knocking out the stores alone gains 10-15 %, their requests' size does not matter.)
+constexpr int EPI_WARP_BYTES = 2 * EPI_CHUNK_BYTES;
+constexpr int EPI_WARP_BYTES_PAIR = 2 * EPI_CHUNK_BYTES;
 constexpr int STAGES_PAIR = 6;                   // pair mode stages half of B per CTA
 constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2;  // 16 KiB
-constexpr int SMEM_BYTES =
-    STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_STAGE_BYTES + 1024 /*align*/ + 256;
-static_assert(STAGES_PAIR * (A_STAGE_BYTES + B_HALF_BYTES) == STAGES * (A_STAGE_BYTES + B_STAGE_BYTES),
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * EPI_WARP_BYTES +
+                           1024 /*align*/ + 256;
+// Pair mode with the fused row push: one pipeline stage less, its 32 KiB hold the rings of the
+// two push warps (warps 10 and 11 of a 384-thread CTA); their small metadata follows the barriers.
+constexpr int STAGES_PAIR_PUSH = STAGES_PAIR - 1;
+constexpr int PUSH_WARPS_PER_CTA = 2;
+constexpr int GEMM_THREADS_PUSH = GEMM_THREADS + 32 * PUSH_WARPS_PER_CTA;
+constexpr int SMEM_BYTES_PUSH = SMEM_BYTES + PUSH_WARPS_PER_CTA * PUSH_META_BYTES;
+static_assert(PUSH_WARPS_PER_CTA * PUSH_RING_BYTES == A_STAGE_BYTES + B_HALF_BYTES,
+              "the push rings take the place of one pipeline stage");
+static_assert(SMEM_BYTES_PUSH <= 227 * 1024, "shared memory budget");
+static_assert(STAGES_PAIR * (A_STAGE_BYTES + B_HALF_BYTES) + EPI_WARPS * EPI_WARP_BYTES_PAIR ==
+                  STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * EPI_WARP_BYTES,
               "both modes use the same shared-memory budget");
 
 struct GemmParams {
@@ -71,6 +87,9 @@ struct GemmParams {
   int pre_is_grad;   // gelu_pre already holds gelu'(x): plain multiply
   int mt_offset;     // rotation of the m-tile order
   int c_multi_rows;  // > 0: rows per destination block of the multi-destination output
+  int signal_count;  // > 0: the last GEMM CTA to finish bumps signal_flags[0 .. signal_count)
+  unsigned* done_counter;
+  unsigned* signal_flags[8];
 };
 
 // Output split over several destinations (row block j of every batch goes to destination j).
@@ -118,22 +137,26 @@ __device__ __forceinline__ void warp_transpose_reduce(float (&v)[32], int lane) 
   }
 }
 
-template <bool PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <bool PAIR, bool PUSHW>
+__global__ void __launch_bounds__(PUSHW ? GEMM_THREADS_PUSH : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_c2,
-                 const __grid_constant__ CMultiMaps cmaps, const GemmParams p) {
+                 const __grid_constant__ CMultiMaps cmaps, const GemmParams p,
+                 const PushParams pp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int NSTAGE = PAIR ? STAGES_PAIR : STAGES;
+  static_assert(PAIR || !PUSHW, "the fused push needs the pair mode's shared-memory layout");
+  constexpr int NSTAGE = PAIR ? (PUSHW ? STAGES_PAIR_PUSH : STAGES_PAIR) : STAGES;
   constexpr int BSTAGE = PAIR ? B_HALF_BYTES : B_STAGE_BYTES;  // B bytes this CTA stages
   constexpr int B_ROWS = PAIR ? BN / 2 : BN;                   // N rows of B this CTA stages
   constexpr int TM = PAIR ? 2 * BM : BM;                       // rows of one tile
   uint8_t* sA = smem;
   uint8_t* sB = smem + NSTAGE * A_STAGE_BYTES;
   uint8_t* sEpi = smem + NSTAGE * (A_STAGE_BYTES + BSTAGE);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + EPI_STAGE_BYTES);
+  constexpr int EPI_WARP = PAIR ? EPI_WARP_BYTES_PAIR : EPI_WARP_BYTES;
+  uint8_t* sPush = sEpi + EPI_WARPS * EPI_WARP;  // rings of the push warps (PUSHW only)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sPush + (PUSHW ? PUSH_WARPS_PER_CTA * PUSH_RING_BYTES : 0));
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
   // Pair mode: rank 0 (the even CTA) leads. `cta` / `ncta` index tiles per CTA or per pair.
@@ -337,12 +360,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
     }
+  } else if (PUSHW && warp >= 2 + EPI_WARPS) {
+    // ------------------------------------------------------------------ row push
+    // Two warps of every CTA deliver this rank's rows to the expert owners (this GPU included)
+    // while the other warps multiply the tiles that have arrived.
+    const int pw = warp - (2 + EPI_WARPS);
+    uint8_t* meta = reinterpret_cast<uint8_t*>(bars) + 256 + pw * PUSH_META_BYTES;
+    push_rows_ring(pp, sPush + pw * PUSH_RING_BYTES, meta, lane,
+                   static_cast<int>(blockIdx.x) * PUSH_WARPS_PER_CTA + pw,
+                   static_cast<int>(gridDim.x) * PUSH_WARPS_PER_CTA, p.status);
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;         // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;  // which 128 columns of the tile this warp handles
-    uint8_t* stage_c = sEpi + (warp - 2) * 2 * EPI_CHUNK_BYTES;
-    uint8_t* stage_c2 = stage_c + EPI_CHUNK_BYTES;
+    uint8_t* stage_c = sEpi + (warp - 2) * EPI_WARP;
+    uint8_t* stage_c2 = stage_c + EPI_WARP / 2;
+    // Wide staging (multi-destination output): two 32-column chunks share one 32 x 64 tile with
+    // 128-byte swizzled rows, spanning both 32 x 32 staging tiles, and leave in one TMA store.
+    const bool wide = p.c_multi_rows > 0;
+    const uint32_t wrow = static_cast<uint32_t>(lane) * 128u;
+    const uint32_t wxor = static_cast<uint32_t>(lane) & 7u;
     // 64B-swizzled position of this lane's row inside a 32 x 32 bf16 staging tile.
     const uint32_t st_row = static_cast<uint32_t>(lane) * 64u;
     const uint32_t st_xor = (static_cast<uint32_t>(lane) >> 1) & 3u;
@@ -403,6 +440,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       };
       if (in_ptr && n0 + half * 128 < p.N) prefetch_input(half * 4);
+      // Writes this lane's 32 values (one row of a chunk) as bf16 into a staging tile.
+      auto stage_row = [&](uint8_t* tile, const float (&x)[32], int c) {
+        const uint32_t cc = static_cast<uint32_t>(c & 1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 q;
+          q.x = pack_bf16x2(x[8 * i + 0], x[8 * i + 1]);
+          q.y = pack_bf16x2(x[8 * i + 2], x[8 * i + 3]);
+          q.z = pack_bf16x2(x[8 * i + 4], x[8 * i + 5]);
+          q.w = pack_bf16x2(x[8 * i + 6], x[8 * i + 7]);
+          if (wide) {
+            *reinterpret_cast<uint4*>(tile + wrow + (((4u * cc + i) ^ wxor) << 4)) = q;
+          } else {
+            *reinterpret_cast<uint4*>(tile + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
+          }
+        }
+      };
 #pragma unroll 1
       for (int c = half * 4; c < half * 4 + 4; ++c) {
         const int col0 = n0 + c * 32;
@@ -450,7 +504,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (p.tma_store) {
           // The staging tiles are reused every chunk: wait until the TMA engine has read the
           // previous contents.
-          if (p.c_multi_rows == 0 || (c & 1) == 0) {
+          if (!wide || (c & 1) == 0) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
           }
@@ -464,15 +518,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             gelu_and_grad_pair(v[i], v[i + 1], a[i], a[i + 1], v[i], v[i + 1]);
           // v now holds gelu' (stored to C2 below); a holds the activation (restored after).
           if (p.tma_store) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 q;
-              q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-              q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-              q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-              q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-              *reinterpret_cast<uint4*>(stage_c2 + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
-            }
+            stage_row(stage_c2, v, c);
           } else if (row_ok) {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0;
 #pragma unroll
@@ -483,15 +529,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           for (int i = 0; i < 32; ++i) v[i] = a[i];
         } else if (p.C2) {
           if (p.tma_store) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 q;
-              q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-              q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-              q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-              q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-              *reinterpret_cast<uint4*>(stage_c2 + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
-            }
+            stage_row(stage_c2, v, c);
           } else if (row_ok) {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C2) + crow + col0;
             if (vec_bf16) {
@@ -586,46 +624,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + i < p.N) v[i] += __bfloat162float(res[i]);
           }
         }
-        if (p.tma_store && p.c_multi_rows > 0) {
-          // Multi-destination output (possibly peer GPUs over NVLink): two 32-column chunks
-          // share one 32 x 64 staging tile (128-byte rows, 128B swizzle; it spans this warp's
-          // C and C2 staging areas, C2 being unused in this mode) and leave in one store, so
-          // the link sees 128-byte row segments instead of 64-byte ones.
-          const uint32_t cc = static_cast<uint32_t>(c & 1);
-          const uint32_t wrow = static_cast<uint32_t>(lane) * 128u;
-          const uint32_t wxor = static_cast<uint32_t>(lane) & 7u;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 q;
-            q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-            q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-            q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-            q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-            *reinterpret_cast<uint4*>(stage_c + wrow + (((4u * cc + i) ^ wxor) << 4)) = q;
-          }
+        if (p.tma_store && wide) {
+          // Two 32-column chunks share one 32 x 64 staging tile (128-byte rows, 128B swizzle) and
+          // leave in one store per output, so that memory (or, for a multi-destination output,
+          // the NVLink to a peer GPU) sees 128-byte row segments instead of 64-byte ones.
+          const int cc = c & 1;
+          stage_row(stage_c, v, c);
           if (cc == 1 || col0 + 32 >= p.N) {
             fence_proxy_async();
             __syncwarp();
-            // Boxes that start past the last row have no destination (and no map): skip them.
             if (lane == 0) {
-              if (row0 < p.M) {
-                const int j = row0 / p.c_multi_rows;
-                tma_store_3d(&cmaps.m[j], smem_u32(stage_c), col0 - 32 * static_cast<int>(cc),
-                             row0 - j * p.c_multi_rows, t.b);
+              const int x0 = col0 - 32 * cc;
+              if (p.c_multi_rows > 0) {
+                // Boxes that start past the last row have no destination (and no map): skip.
+                if (row0 < p.M) {
+                  const int j = row0 / p.c_multi_rows;
+                  tma_store_3d(&cmaps.m[j], smem_u32(stage_c), x0, row0 - j * p.c_multi_rows, t.b);
+                }
+              } else {
+                tma_store_3d(&tma_c, smem_u32(stage_c), x0, row0, t.b);
+                if (p.C2) tma_store_3d(&tma_c2, smem_u32(stage_c2), x0, row0, t.b);
               }
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           }
         } else if (p.tma_store) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 q;
-            q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-            q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-            q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-            q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-            *reinterpret_cast<uint4*>(stage_c + st_row + ((static_cast<uint32_t>(i) ^ st_xor) << 4)) = q;
-          }
+          stage_row(stage_c, v, c);
           fence_proxy_async();  // make the staged tile visible to the TMA engine
           __syncwarp();
           if (lane == 0) {
@@ -696,6 +720,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (p.signal_count > 0 && threadIdx.x == 0) {
+    // Every epilogue warp has waited for its own output stores (bulk wait above, plain stores
+    // are ordered by the barrier). The CTA that takes the last ticket tells the destinations.
+    __threadfence_system();
+    if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
+      *p.done_counter = 0;
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence_system();
+      for (int i = 0; i < p.signal_count; ++i)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.signal_flags[i]), "r"(1u)
+                     : "memory");
+    }
+  }
   if (PAIR) {
     // Neither CTA may free TMEM or exit while its peer can still touch its barriers or TMEM.
     cluster_sync_all();
@@ -735,6 +772,9 @@ int make_bf16_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t ro
   return 0;
 }
 
+int fill_push_params(const VmoePushArgs* a, PushParams* p);      // moe_p2p.cu
+int launch_push_rows_plain(const PushParams& p, cudaStream_t stream);  // moe_p2p.cu
+
 }  // namespace vmoe
 
 extern "C" const char* vmoe_last_error(void) { return vmoe::g_err; }
@@ -761,11 +801,14 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<false>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<false, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_bf16_kernel<true>,
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<true, false>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_bf16_kernel<true, true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_PUSH);
     if (e != cudaSuccess) {
       set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
       return -4;
@@ -783,7 +826,7 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     probe.attrs = &pattr;
     probe.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel<true>, &probe) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel<true, false>, &probe) != cudaSuccess) {
       cudaGetLastError();
       clusters = 0;
     }
@@ -801,9 +844,35 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
       // Pairs pay off once there is at least one 256 x 256 tile per pair of SMs.
       const long long pair_tiles = a->batch * ((a->M + 2 * BM - 1) / (2 * BM)) *
                                    ((a->N + BN - 1) / BN) * (a->split_k > 1 ? a->split_k : 1);
-      pair = a->M >= 2 * BM && a->N >= BN / 2 && pair_tiles >= max_pairs / 2 &&
-             a->a_ready == nullptr;  // tiles gated by peer arrival counters stay one per CTA
+      pair = a->M >= 2 * BM && a->N >= BN / 2 && pair_tiles >= max_pairs / 2;
     }
+  }
+  PushParams pp;
+  memset(&pp, 0, sizeof(pp));
+  bool fused_push = false;
+  if (a->push != nullptr) {
+    const VmoePushArgs* pa = static_cast<const VmoePushArgs*>(a->push);
+    if (pa->groups * pa->e * pa->c > 0) {
+      int prc = fill_push_params(pa, &pp);
+      if (prc) return prc;
+      const char* env_fuse = getenv("VMOE_B200_FUSED_PUSH");  // "0": always a separate launch
+      // Rows that must be scaled (backward of combine) keep two warps per SM busy for longer
+      // than the GEMM runs (measured), so that push stays a launch of its own unless forced
+      // with VMOE_B200_FUSED_PUSH=2.
+      const bool force = env_fuse != nullptr && env_fuse[0] == '2';
+      fused_push = pair && a->a_ready != nullptr &&
+                   push_rows_per_slot(pp.h, pp.weight != nullptr && pp.ybuf_base != nullptr) >= 1 &&
+                   !(env_fuse != nullptr && env_fuse[0] == '0') &&
+                   (pp.weight == nullptr || force);
+      if (!fused_push) {
+        prc = launch_push_rows_plain(pp, stream);
+        if (prc) return prc;
+      }
+    }
+  }
+  if (a->signal_count < 0 || a->signal_count > 8 || (a->signal_count > 0 && !a->done_counter)) {
+    set_error("%s (code %d)", "completion signal needs 1..8 flags and a done_counter", 0);
+    return -1;
   }
   CUtensorMap ma, mb;
   int rc;
@@ -827,12 +896,13 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
                          !(reinterpret_cast<uintptr_t>(a->C) & 15) &&
                          (a->C2 == nullptr || !(reinterpret_cast<uintptr_t>(a->C2) & 15));
   if (tma_store) {
-    rc = make_bf16_map(&mc, a->C, a->N, a->M, a->batch, a->ldc, a->c_batch_stride, 32, 32,
-                       CU_TENSOR_MAP_SWIZZLE_64B);
+    const uint32_t box_w = 32;
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
+    rc = make_bf16_map(&mc, a->C, a->N, a->M, a->batch, a->ldc, a->c_batch_stride, 32, box_w, sw);
     if (rc) return rc;
     if (a->C2) {
-      rc = make_bf16_map(&mc2, a->C2, a->N, a->M, a->batch, a->ldc, a->c_batch_stride, 32, 32,
-                         CU_TENSOR_MAP_SWIZZLE_64B);
+      rc = make_bf16_map(&mc2, a->C2, a->N, a->M, a->batch, a->ldc, a->c_batch_stride, 32, box_w,
+                         sw);
       if (rc) return rc;
     }
   }
@@ -892,6 +962,10 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   p.c2_gelu_grad = a->c2_gelu_grad;
   p.pre_is_grad = a->pre_is_grad;
   p.mt_offset = a->mt_offset > 0 ? static_cast<int>(a->mt_offset % ((a->M + BM - 1) / BM)) : 0;
+  p.signal_count = a->signal_count;
+  p.done_counter = a->done_counter;
+  for (int i = 0; i < a->signal_count; ++i)
+    p.signal_flags[i] = static_cast<unsigned*>(const_cast<void*>(a->signal_flags[i]));
 
   if (pair) {
     const long long num_m2 = (a->M + 2 * BM - 1) / (2 * BM), num_n = (a->N + BN - 1) / BN;
@@ -908,12 +982,14 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
     attr.val.clusterDim.y = 1;
     attr.val.clusterDim.z = 1;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-    cfg.blockDim = dim3(GEMM_THREADS);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.blockDim = dim3(fused_push ? GEMM_THREADS_PUSH : GEMM_THREADS);
+    cfg.dynamicSmemBytes = fused_push ? SMEM_BYTES_PUSH : SMEM_BYTES;
     cfg.stream = stream;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<true>, ma, mb, mc, mc2, cm, p);
+    cudaError_t le =
+        fused_push ? cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<true, true>, ma, mb, mc, mc2, cm, p, pp)
+                   : cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<true, false>, ma, mb, mc, mc2, cm, p, pp);
     if (le != cudaSuccess) {
       set_error("%s (code %d)", cudaGetErrorString(le), static_cast<int>(le));
       return -5;
@@ -922,9 +998,10 @@ extern "C" int vmoe_gemm_bf16(const VmoeGemmArgs* a, vmoe_stream_t stream_) {
   }
   const long long num_m = (a->M + BM - 1) / BM, num_n = (a->N + BN - 1) / BN;
   const long long tiles = a->batch * num_m * num_n * p.split_k;
-  int max_ctas = a->num_sms > 0 ? a->num_sms : sm_count;
+  int max_ctas = a->num_sms > 0 && a->num_sms < sm_count ? a->num_sms : sm_count;
   int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
-  gemm_bf16_kernel<false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, cm, p);
+  gemm_bf16_kernel<false, false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, mc2, cm, p,
+                                                                             pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));

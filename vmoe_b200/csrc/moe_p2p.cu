@@ -21,30 +21,15 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
+#include "moe_push.cuh"
 #include "ptx_sm100.cuh"
 #include "vmoe_api.h"
 
 namespace vmoe {
 
 void set_error(const char* fmt, const char* a, int code);
-
-constexpr int PUSH_ROWS = 128;  // destination rows per chunk (= GEMM tile height)
-
-struct PushParams {
-  const __nv_bfloat16* x;       // (G, S, H) local rows (tokens or dy)
-  const int* slot_pair;         // (G, E, C)
-  const float* weight;          // (G, S, K) or NULL
-  const unsigned long long* dst_base;   // [E] address of this rank's block of expert e's buffer
-  const unsigned long long* flag_base;  // [E] address of expert e's tile counters (on its owner)
-  const unsigned long long* ybuf_base;  // [E] local expert outputs (gate gradient) or NULL
-  float* dgate;                 // (G, S, K) or NULL
-  int g, s, e, c, k, h;
-  int el;         // experts per rank
-  int ep;         // ranks in the expert group
-  int rank;       // this rank's index in the group
-  int row0;       // first row of this rank's block inside an expert buffer (= rank * G * C)
-};
 
 __device__ __forceinline__ void unpack8p(const uint4& q, float (&f)[8]) {
   float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z),
@@ -163,6 +148,56 @@ __global__ void wait_counters_kernel(const unsigned* counters, int n, unsigned t
   }
 }
 
+// The bulk-copy push (moe_push.cuh) as a kernel of its own: the body that the GEMM kernel runs in
+// two extra warps of each of its CTAs, launched alone so that it can be tested and timed in
+// isolation.
+constexpr int PUSH_KERNEL_WARPS = 8;
+__global__ void __launch_bounds__(PUSH_KERNEL_WARPS * 32)
+push_rows_bulk_kernel(const PushParams p, unsigned* status) {
+  extern __shared__ uint8_t push_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(push_smem_raw) + 127) &
+                                             ~static_cast<uintptr_t>(127));
+  const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  push_rows_ring(p, smem + warp * PUSH_RING_BYTES,
+                 smem + nwarps * PUSH_RING_BYTES + warp * PUSH_META_BYTES,
+                 threadIdx.x & 31, blockIdx.x * nwarps + warp, gridDim.x * nwarps, status);
+}
+
+struct SignalAddrs {
+  unsigned* f[16];
+};
+__global__ void signal_multi_kernel(const SignalAddrs a, int n, unsigned value) {
+  __threadfence_system();
+  if (threadIdx.x < n)
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.f[threadIdx.x]), "r"(value)
+                 : "memory");
+}
+
+int fill_push_params(const VmoePushArgs* a, PushParams* p) {
+  if (a->h % 8 || a->e != a->experts_per_rank * a->ep) {
+    set_error("%s (code %d)", "push_rows: need h % 8 == 0 and e == experts_per_rank * ep", 0);
+    return -1;
+  }
+  p->x = static_cast<const __nv_bfloat16*>(a->x);
+  p->slot_pair = a->slot_pair;
+  p->weight = a->weight;
+  p->dst_base = reinterpret_cast<const unsigned long long*>(a->dst_base);
+  p->flag_base = reinterpret_cast<const unsigned long long*>(a->flag_base);
+  p->ybuf_base = reinterpret_cast<const unsigned long long*>(a->ybuf_base);
+  p->dgate = a->dgate;
+  p->g = static_cast<int>(a->groups);
+  p->s = static_cast<int>(a->s);
+  p->e = static_cast<int>(a->e);
+  p->c = static_cast<int>(a->c);
+  p->k = static_cast<int>(a->k);
+  p->h = static_cast<int>(a->h);
+  p->el = static_cast<int>(a->experts_per_rank);
+  p->ep = static_cast<int>(a->ep);
+  p->rank = static_cast<int>(a->rank);
+  p->row0 = static_cast<int>(a->rank * a->groups * a->c);
+  return 0;
+}
+
 }  // namespace vmoe
 
 using namespace vmoe;
@@ -228,6 +263,83 @@ extern "C" int vmoe_wait_counters(const uint32_t* counters, int32_t n, uint32_t 
   }
   wait_counters_kernel<<<1, n, 0, static_cast<cudaStream_t>(stream_)>>>(
       counters, n, target, status, limit_cycles > 0 ? limit_cycles : kWaitLimitCycles);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("%s (code %d)", cudaGetErrorString(err), static_cast<int>(err));
+    return -5;
+  }
+  return 0;
+}
+
+extern "C" int32_t vmoe_moe_push_bulk_supported(int64_t h, int32_t with_gate_gradient) {
+  return push_rows_per_slot(static_cast<int>(h), with_gate_gradient != 0) >= 1 ? 1 : 0;
+}
+
+extern "C" int vmoe_moe_push_rows_bulk(const VmoePushArgs* a, int32_t ctas, uint32_t* status,
+                                       vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->groups * a->e * a->c == 0) return 0;
+  PushParams p;
+  int rc = fill_push_params(a, &p);
+  if (rc) return rc;
+  if (push_rows_per_slot(p.h, p.weight != nullptr && p.ybuf_base != nullptr) < 1) {
+    set_error("%s (code %d)", "push_rows_bulk: rows too long for the shared-memory ring", p.h);
+    return -1;
+  }
+  const int smem = PUSH_KERNEL_WARPS * (PUSH_RING_BYTES + PUSH_META_BYTES) + 128;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(push_rows_bulk_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_error("%s (code %d)", cudaGetErrorString(e), static_cast<int>(e));
+      return -4;
+    }
+    attr_set = true;
+  }
+  if (ctas <= 0) ctas = 37;
+  int warps = PUSH_KERNEL_WARPS;
+  if (const char* w = getenv("VMOE_B200_PUSH_KERNEL_WARPS")) {  // 1..8, for timing experiments
+    const int v = atoi(w);
+    if (v >= 1 && v <= PUSH_KERNEL_WARPS) warps = v;
+  }
+  push_rows_bulk_kernel<<<ctas, warps * 32, smem, stream>>>(p, status);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("%s (code %d)", cudaGetErrorString(err), static_cast<int>(err));
+    return -5;
+  }
+  return 0;
+}
+
+// The plain (SIMT) push as a launch for callers inside the library (the GEMM falls back to it
+// when the fused form does not apply).
+namespace vmoe {
+int launch_push_rows_plain(const PushParams& p, cudaStream_t stream) {
+  const long long block_rows = static_cast<long long>(p.g) * p.c;
+  const long long total = p.e * ((block_rows + PUSH_ROWS - 1) / PUSH_ROWS);
+  if (total <= 0) return 0;
+  const int grid = static_cast<int>(total < 148 * 8 ? total : 148 * 8);
+  push_rows_kernel<<<grid, PUSH_THREADS, 0, stream>>>(p);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("%s (code %d)", cudaGetErrorString(err), static_cast<int>(err));
+    return -5;
+  }
+  return 0;
+}
+}  // namespace vmoe
+
+extern "C" int vmoe_signal_multi(const uint64_t* flags, int32_t n, uint32_t value,
+                                 vmoe_stream_t stream_) {
+  if (n <= 0) return 0;
+  if (n > 16) {
+    set_error("%s (code %d)", "signal_multi: at most 16 flags", n);
+    return -1;
+  }
+  SignalAddrs a;
+  for (int i = 0; i < 16; ++i) a.f[i] = i < n ? reinterpret_cast<unsigned*>(flags[i]) : nullptr;
+  signal_multi_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(a, n, value);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("%s (code %d)", cudaGetErrorString(err), static_cast<int>(err));

@@ -29,6 +29,7 @@ typedef void* vmoe_stream_t;  // cudaStream_t
 //   v += residual[row, col]              (residual != NULL; bf16, leading dim ldr)
 //   colsum[col] += sum over rows of v    (colsum != NULL; fp32 atomics)
 //   C[row, col] = v                      (bf16 or fp32 store, or fp32 atomic add)
+struct VmoePushArgs;
 typedef struct VmoeGemmArgs {
   const void* A;
   const void* B;
@@ -60,6 +61,19 @@ typedef struct VmoeGemmArgs {
   const void* c_multi[8];
   int32_t c_multi_count;
   int64_t c_multi_rows;
+  // Fused dispatch: when `push` is set (a VmoePushArgs), the row push (moe_push.cuh) runs inside
+  // this launch, in two extra warps of every CTA, while the MMA and epilogue warps consume the
+  // A tiles gated by the a_ready counters that the push (of this and of the peer GPUs)
+  // advances. Needs the CTA-pair mode and rows that fit the push ring; otherwise the push is
+  // launched as a kernel of its own in front of the GEMM (same result).
+  const void* push;
+  int32_t push_ctas;  // unused (kept for layout compatibility)
+  // Completion signal: when signal_count > 0, the last GEMM CTA to finish (all its output
+  // stores complete) adds 1, release at system scope, to each signal_flags[i] (device addresses,
+  // local or peer). done_counter: a zero-initialised device word private to the caller.
+  const void* signal_flags[8];
+  int32_t signal_count;
+  unsigned* done_counter;
 } VmoeGemmArgs;
 
 VMOE_API int vmoe_gemm_bf16(const VmoeGemmArgs* args, vmoe_stream_t stream);
@@ -98,16 +112,6 @@ VMOE_API int vmoe_layernorm_bwd_strided(const void* dy, const void* x, const flo
                                         int64_t h, int64_t inner, int64_t dy_outer,
                                         int64_t x_outer, int64_t dx_outer, vmoe_stream_t stream);
 
-// No-allocation variant of vmoe_layernorm_bwd (this entry point has no counterpart in the
-// reference, which leaves all memory management to XLA). The partial sums of dgamma / dbeta go
-// to a static device array inside the library (3.5 MiB, hidden sizes up to 1024) instead of a
-// caller-provided scratch buffer, and the call invokes no allocating routine.
-//  * The first call on each device resolves the array's device address (a host-side set-up
-//    step); make that call before any stream capture.
-//  * All calls on a device share the one array. It keeps the contents of the last call; nothing
-//    in it has to be zero on entry, because every launch overwrites the rows it later reads.
-//  * Calls that overlap in time on one device (different streams or threads) race on the array;
-//    serialise them.
 // All-reduce (sum) of the fp32 range [offset, offset + count) of a symmetric gradient buffer
 // over `world` ranks with peer loads (two kernels: reduce own slice, gather the others).
 // bufs / flags: host arrays of `world` device addresses (gradient buffer base and counter base
@@ -121,6 +125,16 @@ VMOE_API int vmoe_allreduce_range(const uint64_t* bufs, const uint64_t* flags, i
                                   uint32_t* status, int32_t ctas, int64_t limit_cycles,
                                   vmoe_stream_t stream);
 
+// No-allocation variant of vmoe_layernorm_bwd (this entry point has no counterpart in the
+// reference, which leaves all memory management to XLA). The partial sums of dgamma / dbeta go
+// to a static device array inside the library (3.5 MiB, hidden sizes up to 1024) instead of a
+// caller-provided scratch buffer, and the call invokes no allocating routine.
+//  * The first call on each device resolves the array's device address (a host-side set-up
+//    step); make that call before any stream capture.
+//  * All calls on a device share the one array. It keeps the contents of the last call; nothing
+//    in it has to be zero on entry, because every launch overwrites the rows it later reads.
+//  * Calls that overlap in time on one device (different streams or threads) race on the array;
+//    serialise them.
 //  * Returns -1 with a message in vmoe_last_error() when h > 1024.
 VMOE_API int vmoe_layernorm_bwd_static(const void* dy, const void* x, const float* gamma,
                                        const float* mean, const float* rstd, const void* dres,
@@ -217,6 +231,29 @@ VMOE_API int vmoe_moe_push_rows(const void* x, const int32_t* slot_pair, const f
                                 int64_t e, int64_t c, int64_t k, int64_t h,
                                 int64_t experts_per_rank, int64_t ep, int64_t rank,
                                 vmoe_stream_t stream);
+// The same push with bulk asynchronous copies (global -> shared-memory ring -> owner's buffer),
+// one ring per warp. This is the body that vmoe_gemm_bf16 runs in two extra warps of each of
+// its CTAs when VmoeGemmArgs.push is set; as a kernel of its own (`ctas` CTAs of 8 warps) it
+// serves tests and timing. flag_base[e][tile] counters as for vmoe_moe_push_rows, in steps of
+// at most 32 rows. Rows must fit the ring: vmoe_moe_push_bulk_supported(h, with y rows).
+typedef struct VmoePushArgs {
+  const void* x;
+  const int32_t* slot_pair;
+  const float* weight;
+  const uint64_t* dst_base;
+  const uint64_t* flag_base;
+  const uint64_t* ybuf_base;
+  float* dgate;
+  int64_t groups, s, e, c, k, h;
+  int64_t experts_per_rank, ep, rank;
+} VmoePushArgs;
+VMOE_API int32_t vmoe_moe_push_bulk_supported(int64_t h, int32_t with_gate_gradient);
+VMOE_API int vmoe_moe_push_rows_bulk(const VmoePushArgs* args, int32_t ctas, uint32_t* status,
+                                     vmoe_stream_t stream);
+// flags[i] += value for n <= 16 addresses (host array of device addresses, local or peer) in
+// one launch, with a system-scope release ordered after all earlier work of the stream.
+VMOE_API int vmoe_signal_multi(const uint64_t* flags, int32_t n, uint32_t value,
+                               vmoe_stream_t stream);
 // *flag += value with a system-scope release, ordered after all earlier work of the stream.
 VMOE_API int vmoe_signal(uint32_t* flag, uint32_t value, vmoe_stream_t stream);
 // Blocks the stream until counters[i] >= target for all i < n; gives up after limit_cycles

@@ -12,7 +12,8 @@ import os
 import threading
 
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG_DIR, "libvmoe_b200.so")
+# VMOE_B200_LIB names another build of the same library (kernel experiments).
+LIB_PATH = os.environ.get("VMOE_B200_LIB") or os.path.join(_PKG_DIR, "libvmoe_b200.so")
 
 _lib = None
 _lock = threading.Lock()
@@ -59,6 +60,23 @@ class GemmArgs(ctypes.Structure):
       ("c_multi", ctypes.c_void_p * 8),
       ("c_multi_count", ctypes.c_int32),
       ("c_multi_rows", ctypes.c_int64),
+      ("push", ctypes.c_void_p),
+      ("push_ctas", ctypes.c_int32),
+      ("signal_flags", ctypes.c_void_p * 8),
+      ("signal_count", ctypes.c_int32),
+      ("done_counter", ctypes.c_void_p),
+  ]
+
+
+class PushArgs(ctypes.Structure):
+  """Mirror of ``VmoePushArgs`` (row push of the expert-parallel dispatch)."""
+  _fields_ = [
+      ("x", ctypes.c_void_p), ("slot_pair", ctypes.c_void_p), ("weight", ctypes.c_void_p),
+      ("dst_base", ctypes.c_void_p), ("flag_base", ctypes.c_void_p),
+      ("ybuf_base", ctypes.c_void_p), ("dgate", ctypes.c_void_p),
+      ("groups", ctypes.c_int64), ("s", ctypes.c_int64), ("e", ctypes.c_int64),
+      ("c", ctypes.c_int64), ("k", ctypes.c_int64), ("h", ctypes.c_int64),
+      ("experts_per_rank", ctypes.c_int64), ("ep", ctypes.c_int64), ("rank", ctypes.c_int64),
   ]
 
 

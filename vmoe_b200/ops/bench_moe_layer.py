@@ -24,10 +24,10 @@ class _Mlp:
   dropout_rate = 0.0
 
 
-def forward_phases(moe_ops, disp, mlp, x, res, ex, c, iters):
-  """The launches of the peer-memory forward (``moe_ops._P2PMoeFn.forward``) with a CUDA event
-  between them; returns mean milliseconds per phase on this rank."""
-  from vmoe_b200.ops.functional import bf16_shadow
+def layer_phases(moe_ops, disp, mlp, x, res, dy, ex, c, iters):
+  """The launches of the peer-memory layer (``moe_ops._P2PMoeFn``), forward then backward, with
+  a CUDA event between them; returns mean milliseconds per phase on this rank."""
+  from vmoe_b200.ops.functional import _wgrad_split, bf16_shadow, bias_grad, wgrad
   from vmoe_b200.ops.gemm import ACT_GELU, gemm
   g, s, h = x.shape
   e, k = disp.num_experts, disp.expert.shape[-1]
@@ -35,33 +35,62 @@ def forward_phases(moe_ops, disp, mlp, x, res, ex, c, iters):
   comm = moe_ops.layer_comm(mlp, ex, e, r, h, x.device)
   ep, el, rank = comm.ep, comm.el, comm.rank
   w1h, w2h = bf16_shadow(mlp.w1), bf16_shadow(mlp.w2)
+  m = mlp.w1.shape[1]
   gate = disp.combine_weights.detach().float().contiguous()
-  names = ["barrier", "push_rows", "gemm1_gated", "gemm2_to_peers", "signal_wait", "combine"]
+  names = ["wait_free", "push+gemm1", "gemm2_to_peers", "wait_y", "combine",
+           "push_dy+dgrad", "dx_to_peers", "bias+wgrads", "signal_free+wait_dx", "combine_dx"]
   total = {n: 0.0 for n in names}
+  xd, dyd = x.detach(), dy.detach()
   with torch.no_grad():
     for it in range(iters + 2):
       ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
       ev[0].record()
-      comm.buf.barrier()
-      for key in ("x", "y"):
+      if comm.epoch["free"] > 0:
+        moe_ops.wait_counters(comm.ffree, ep, comm.epoch["free"], comm.status)
+      for key in ("x", "y", "dy", "dx"):
         comm.epoch[key] += 1
       ev[1].record()
-      moe_ops.push_rows(x, disp.slot_pair, None, comm.push_x, comm.flag_x, None, None, g, s, e, c,
-                        k, h, el, ep, rank)
+      pre = torch.empty(el, ep * r, m, dtype=torch.bfloat16, device=x.device)
+      pa = moe_ops.push_args(xd, disp.slot_pair, None, comm.push_x, comm.flag_x, None, None, g, s,
+                             e, c, k, h, el, ep, rank)
+      hid = gemm(comm.xe, w1h, bias=mlp.b1, act=ACT_GELU, out_pre=pre, out_pre_is_grad=True,
+                 a_ready=comm.fx, a_ready_epoch=comm.epoch["x"], status=comm.status,
+                 mt_offset=comm.mt_offset, push=pa)
       ev[2].record()
-      hid = gemm(comm.xe, w1h, bias=mlp.b1, act=ACT_GELU, a_ready=comm.fx,
-                 a_ready_epoch=comm.epoch["x"], status=comm.status, mt_offset=comm.mt_offset)
-      ev[3].record()
       gemm(hid, w2h, bias=mlp.b2, out_multi=[comm.home_out("YB", src) for src in range(ep)],
-           mt_offset=comm.mt_offset)
-      ev[4].record()
-      for src in range(ep):
-        moe_ops.signal(comm.done_flag_addr("FY", src))
+           mt_offset=comm.mt_offset, signal_flags=comm.done_flag_addrs("FY"),
+           done_counter=comm.done[0:1])
+      ev[3].record()
       moe_ops.wait_counters(comm.fy, ep, comm.epoch["y"], comm.status)
-      ev[5].record()
-      out = torch.empty_like(x)
+      ev[4].record()
+      out = torch.empty_like(xd)
       moe_ops.combine_rows(comm.yb_table, disp.expert, disp.slot, gate, res, out, g, s, e, c, k, h)
+      ev[5].record()
+      # ---- backward
+      dgate = torch.zeros(g, s, k, dtype=torch.float32, device=x.device)
+      pa = moe_ops.push_args(dyd, disp.slot_pair, gate, comm.push_dy, comm.flag_dy, comm.yb_table,
+                             dgate, g, s, e, c, k, h, el, ep, rank)
+      db1 = torch.zeros(el, m, dtype=torch.float32, device=x.device)
+      dpre = gemm(comm.dye, w2h, b_mn_major=True, gelu_pre=pre, gelu_pre_is_grad=True, colsum=db1,
+                  a_ready=comm.fdy, a_ready_epoch=comm.epoch["dy"], status=comm.status,
+                  mt_offset=comm.mt_offset, push=pa)
       ev[6].record()
+      gemm(dpre, w1h, b_mn_major=True, out_multi=[comm.home_out("DXB", src) for src in range(ep)],
+           mt_offset=comm.mt_offset, signal_flags=comm.done_flag_addrs("FDX"),
+           done_counter=comm.done[1:2])
+      ev[7].record()
+      mlp.w1.grad = mlp.w2.grad = mlp.b2.grad = None
+      bias_grad(comm.dye, mlp.b2)
+      wgrad(comm.dye, hid, mlp.w2, split_k=_wgrad_split(h, m, ep * r) if el == 1 else 1)
+      wgrad(dpre, comm.xe, mlp.w1, split_k=_wgrad_split(m, h, ep * r) if el == 1 else 1)
+      ev[8].record()
+      comm.epoch["free"] += 1
+      moe_ops.signal_multi(comm.done_flag_addrs("FFREE"))
+      moe_ops.wait_counters(comm.fdx, ep, comm.epoch["dx"], comm.status)
+      ev[9].record()
+      dx = torch.empty_like(xd)
+      moe_ops.combine_rows(comm.dxb_table, disp.expert, disp.slot, None, None, dx, g, s, e, c, k, h)
+      ev[10].record()
       torch.cuda.synchronize()
       if it >= 2:
         for i, n in enumerate(names):
@@ -83,9 +112,13 @@ def main():
                   help="measured sustained cuBLAS bf16 throughput used as the compute roof")
   ap.add_argument("--link-gbs", type=float, default=770.0)
   ap.add_argument("--phases", action="store_true",
-                  help="also time the launches of the peer-memory forward one by one")
+                  help="also time the launches of the peer-memory layer one by one")
+  ap.add_argument("--separate-push", action="store_true",
+                  help="launch the row push as a kernel of its own in front of the GEMM")
   args = ap.parse_args()
   os.environ["VMOE_B200_P2P"] = "1" if args.path == "p2p" else "0"
+  if args.separate_push:
+    os.environ["VMOE_B200_FUSED_PUSH"] = "0"
   from vmoe_b200.ops import moe_ops
   from vmoe_b200.parallel import mesh as mesh_lib
   from vmoe_b200.parallel.exchange import ExpertExchange
@@ -136,11 +169,11 @@ def main():
     return float(t.item())
 
   if args.phases and args.path == "p2p" and ex.size > 1:
-    phases = forward_phases(moe_ops, disp, mlp, x, res, ex, c, args.iters)
+    phases = layer_phases(moe_ops, disp, mlp, x, res, dy, ex, c, args.iters)
     t = torch.tensor(list(phases.values()), device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
-      print(json.dumps({"forward_phases_ms_max_over_ranks":
+      print(json.dumps({"phases_ms_max_over_ranks":
                         dict(zip(phases.keys(), [round(v, 4) for v in t.tolist()]))}))
   with torch.no_grad():
     t_fwd = timed(fwd)

@@ -77,7 +77,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
          a_ready_epoch: int = 0, status: Optional[torch.Tensor] = None,
          num_sms: int = 0, out_pre_is_grad: bool = False,
          gelu_pre_is_grad: bool = False, mt_offset: int = 0,
-         cta_pair: int = 0, out_multi=None) -> torch.Tensor:
+         cta_pair: int = 0, out_multi=None, push=None,
+         signal_flags=None, done_counter: Optional[torch.Tensor] = None) -> torch.Tensor:
   """``out = epilogue(a @ b^T)``; see ``csrc/vmoe_api.h`` for the epilogue order."""
   if not a.is_cuda:
     return gemm_reference(a, b, a_mn_major=a_mn_major, b_mn_major=b_mn_major, bias=bias,
@@ -170,6 +171,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
     args.c_multi_rows = d0.shape[1]
     args.ldc = d0.stride(1)
     args.c_batch_stride = d0.stride(0) if batch > 1 else 0
+  if push is not None:
+    # ``push``: a ``_lib.PushArgs``; two warps of every CTA of the launch deliver rows to the
+    # expert owners while the others consume arrived tiles (``a_ready``). Where the fused form
+    # does not apply the library runs the push as a launch of its own first.
+    args.push = ctypes.cast(ctypes.pointer(push), ctypes.c_void_p)
+  if signal_flags:
+    # Device addresses (local or peer) that receive +1 once every output tile is stored.
+    assert len(signal_flags) <= 8 and done_counter is not None
+    for j, addr in enumerate(signal_flags):
+      args.signal_flags[j] = int(addr)
+    args.signal_count = len(signal_flags)
+    args.done_counter = done_counter.data_ptr()
   rc = _lib.lib().vmoe_gemm_bf16(ctypes.byref(args), ctypes.c_void_p(_lib.stream_ptr()))
   _lib.check(rc, "vmoe_gemm_bf16")
   _lib.count_launch()

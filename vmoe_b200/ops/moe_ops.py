@@ -20,7 +20,8 @@ import torch.distributed as dist
 
 from vmoe_b200 import moe as moe_core
 from vmoe_b200.ops import _lib
-from vmoe_b200.ops.functional import _grad_target, bf16_shadow, bias_grad, wgrad
+from vmoe_b200.ops.functional import (_grad_target, _wgrad_split, bf16_shadow, bias_grad,
+                                       wgrad)
 from vmoe_b200.ops.gemm import ACT_GELU, gemm
 from vmoe_b200.parallel.exchange import ExpertExchange, LOCAL_EXCHANGE
 
@@ -133,6 +134,35 @@ def push_rows(x, slot_pair, weight, dst_table, flag_table, ybuf_table, dgate, g,
   _lib.count_launch()
 
 
+def push_args(x, slot_pair, weight, dst_table, flag_table, ybuf_table, dgate, g, s, e, c, k, h,
+              el, ep, rank) -> "_lib.PushArgs":
+  """Arguments of the row push for the GEMM's push CTAs (``gemm(..., push=...)``) or for
+  ``push_rows_bulk``. The tensors must stay alive until the launch that uses them is enqueued."""
+  a = _lib.PushArgs()
+  a.x, a.slot_pair, a.weight = x.data_ptr(), slot_pair.data_ptr(), _lib.ptr(weight)
+  a.dst_base, a.flag_base = dst_table.data_ptr(), _lib.ptr(flag_table)
+  a.ybuf_base, a.dgate = _lib.ptr(ybuf_table), _lib.ptr(dgate)
+  a.groups, a.s, a.e, a.c, a.k, a.h = g, s, e, c, k, h
+  a.experts_per_rank, a.ep, a.rank = el, ep, rank
+  return a
+
+
+def push_rows_bulk(args: "_lib.PushArgs", ctas: int = 37, status=None):
+  """The bulk-copy row push as a launch of its own (``csrc/moe_push.cuh``)."""
+  rc = _lib.lib().vmoe_moe_push_rows_bulk(ctypes.byref(args), ctypes.c_int32(ctas),
+                                          _vp(_lib.ptr(status)), _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_moe_push_rows_bulk")
+  _lib.count_launch()
+
+
+def signal_multi(addrs, value: int = 1):
+  arr = (ctypes.c_uint64 * len(addrs))(*[int(a) for a in addrs])
+  rc = _lib.lib().vmoe_signal_multi(arr, ctypes.c_int32(len(addrs)), ctypes.c_uint32(value),
+                                    _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_signal_multi")
+  _lib.count_launch()
+
+
 def signal(addr: int, value: int = 1):
   rc = _lib.lib().vmoe_signal(_vp(addr), ctypes.c_uint32(value), _vp(_lib.stream_ptr()))
   _lib.check(rc, "vmoe_signal")
@@ -166,8 +196,9 @@ class LayerComm:
     fl_src = 256
     self.off = {"XE": 0, "YB": blk, "DYE": 2 * blk, "DXB": 3 * blk,
                 "FX": 4 * blk, "FDY": 4 * blk + fl_tiles, "FY": 4 * blk + 2 * fl_tiles,
-                "FDX": 4 * blk + 2 * fl_tiles + fl_src}
-    self.buf = symm.SymmetricBuffer(4 * blk + 2 * fl_tiles + 2 * fl_src, exchange.group, device)
+                "FDX": 4 * blk + 2 * fl_tiles + fl_src,
+                "FFREE": 4 * blk + 2 * fl_tiles + 2 * fl_src}
+    self.buf = symm.SymmetricBuffer(4 * blk + 2 * fl_tiles + 3 * fl_src, exchange.group, device)
     self.rank = self.buf.rank
     b = self.buf
     self.xe = b.local(self.off["XE"], (self.el, ep * r, h), torch.bfloat16)
@@ -178,8 +209,12 @@ class LayerComm:
     self.fdy = b.local(self.off["FDY"], (self.el * self.tiles,), torch.int32)
     self.fy = b.local(self.off["FY"], (64,), torch.int32)
     self.fdx = b.local(self.off["FDX"], (64,), torch.int32)
+    # ffree[src]: backward passes after which rank src no longer reads what this rank pushed
+    # into its XE / DYE buffers; the next forward waits for it instead of a group barrier.
+    self.ffree = b.local(self.off["FFREE"], (64,), torch.int32)
     self.status = torch.zeros(1, dtype=torch.int32, device=device)
-    self.epoch = {"x": 0, "y": 0, "dy": 0, "dx": 0}
+    self.done = torch.zeros(2, dtype=torch.int32, device=device)  # GEMM completion tickets
+    self.epoch = {"x": 0, "y": 0, "dy": 0, "dx": 0, "free": 0}
 
     def table(data_key, flag_key):
       dst, flg = [], []
@@ -203,6 +238,11 @@ class LayerComm:
 
   def done_flag_addr(self, key: str, src: int) -> int:
     return self.buf.ptrs[src] + self.off[key] + self.rank * 4
+
+  def done_flag_addrs(self, key: str):
+    """This rank's completion flag on every rank of the group, own rank first: the flag whose
+    owner is this GPU is bumped without crossing the link."""
+    return [self.done_flag_addr(key, (self.rank + i) % self.ep) for i in range(self.ep)]
 
 
 _LAYER_COMMS: dict = {}
@@ -247,26 +287,30 @@ class _P2PMoeFn(torch.autograd.Function):
     gate = gate.contiguous().float()
     w1h, w2h = bf16_shadow(w1), bf16_shadow(w2)
     m = w1.shape[1]
-    # All ranks are past their previous use of this layer's buffers.
-    comm.buf.barrier()
+    # Every peer is past the reads of what this rank pushed last time (its previous backward
+    # pass through this layer): a counter wait that is normally satisfied long before, instead
+    # of a barrier over the group.
+    if comm.epoch["free"] > 0:
+      wait_counters(comm.ffree, ep, comm.epoch["free"], comm.status)
     for key in ("x", "y"):
       comm.epoch[key] += 1
-    push_rows(x, slot_pair, None, comm.push_x, comm.flag_x, None, None, g, s, e, c, k, h, el, ep,
-              rank)
     need = any(ctx.needs_input_grad)
     pre = torch.empty(el, ep * r, m, dtype=torch.bfloat16, device=x.device) if need else None
+    pargs = push_args(x, slot_pair, None, comm.push_x, comm.flag_x, None, None, g, s, e, c, k, h,
+                      el, ep, rank)
+    # Dispatch + first expert GEMM in one launch: two warps of every CTA send this rank's rows
+    # to the expert owners while the other warps multiply the tiles that have arrived.
     hid = gemm(comm.xe, w1h, bias=b1, act=ACT_GELU, out_pre=pre, out_pre_is_grad=True,
                a_ready=comm.fx, a_ready_epoch=comm.epoch["x"], status=comm.status,
-               mt_offset=comm.mt_offset)
+               mt_offset=comm.mt_offset, push=pargs)
     if r % 32 == 0 and ep <= 8:
       # One GEMM over all rows; every 32-row output box is TMA-stored straight into the home
-      # buffer of the rank its rows came from.
+      # buffer of the rank its rows came from, and the last CTA to finish tells every home rank.
       # mt_offset: rank r starts with the rows of source r, so at any moment the ranks store to
       # different destinations instead of all converging on the same GPU's link.
       gemm(hid, w2h, bias=b2, out_multi=[comm.home_out("YB", src) for src in range(ep)],
-           mt_offset=comm.mt_offset)
-      for src in range(ep):
-        signal(comm.done_flag_addr("FY", src))
+           mt_offset=comm.mt_offset, signal_flags=comm.done_flag_addrs("FY"),
+           done_counter=comm.done[0:1])
     else:
       for i in range(ep):
         src = (rank + i) % ep
@@ -294,22 +338,23 @@ class _P2PMoeFn(torch.autograd.Function):
     for key in ("dy", "dx"):
       comm.epoch[key] += 1
     dgate = torch.zeros(g, s, k, dtype=torch.float32, device=dev)
-    push_rows(dy, slot_pair, gate, comm.push_dy, comm.flag_dy, comm.yb_table, dgate, g, s, e, c, k,
-              h, el, ep, rank)
+    pargs = push_args(dy, slot_pair, gate, comm.push_dy, comm.flag_dy, comm.yb_table, dgate, g, s,
+                      e, c, k, h, el, ep, rank)
     b1, b2 = ctx.biases
     tgt = _grad_target(b1)
     db1 = tgt if tgt is not None else torch.zeros(el, m, dtype=torch.float32, device=dev)
+    # Backward of combine (gate-scaled dy rows and the gate gradients) pushed by two warps of
+    # every CTA of the hidden-gradient GEMM, which consumes the rows as they arrive.
     dpre = gemm(comm.dye, w2h, b_mn_major=True, gelu_pre=pre, gelu_pre_is_grad=True, colsum=db1,
                 a_ready=comm.fdy, a_ready_epoch=comm.epoch["dy"], status=comm.status,
-                mt_offset=comm.mt_offset)
+                mt_offset=comm.mt_offset, push=pargs)
     if tgt is not None:
       db1 = None
     # dX first: its tiles travel home over NVLink while the weight-gradient GEMMs below run.
     if r % 32 == 0 and ep <= 8:
       gemm(dpre, w1h, b_mn_major=True,
-           out_multi=[comm.home_out("DXB", src) for src in range(ep)], mt_offset=comm.mt_offset)
-      for src in range(ep):
-        signal(comm.done_flag_addr("FDX", src))
+           out_multi=[comm.home_out("DXB", src) for src in range(ep)], mt_offset=comm.mt_offset,
+           signal_flags=comm.done_flag_addrs("FDX"), done_counter=comm.done[1:2])
     else:
       for i in range(ep):
         src = (rank + i) % ep
@@ -318,8 +363,12 @@ class _P2PMoeFn(torch.autograd.Function):
         signal(comm.done_flag_addr("FDX", src))
     # Every tile of dye has arrived once the dpre GEMM above has run.
     db2 = bias_grad(comm.dye, b2)
-    dw2 = wgrad(comm.dye, hid, w2)
-    dw1 = wgrad(dpre, comm.xe, w1)
+    # One expert per GPU leaves only 72 output tiles: split the long contraction over two CTAs.
+    dw2 = wgrad(comm.dye, hid, w2, split_k=_wgrad_split(h, m, ep * r) if el == 1 else 1)
+    dw1 = wgrad(dpre, comm.xe, w1, split_k=_wgrad_split(m, h, ep * r) if el == 1 else 1)
+    # The rows that the peers pushed into XE / DYE have been read for the last time.
+    comm.epoch["free"] += 1
+    signal_multi(comm.done_flag_addrs("FFREE"))
     wait_counters(comm.fdx, ep, comm.epoch["dx"], comm.status)
     dx = torch.empty(g, s, h, dtype=torch.bfloat16, device=dev)
     combine_rows(comm.dxb_table, expert, slot, None, None, dx, g, s, e, c, k, h)
