@@ -1,4 +1,6 @@
 """Elementwise / MoE / loss / optimizer kernels vs PyTorch fp32 references."""
+import math
+
 import pytest
 import torch
 import torch.nn.functional as F
@@ -167,23 +169,102 @@ def test_graft_smoke():
   __graft_entry__.smoke()
 
 
-@pytest.mark.parametrize("b,t,h", [(2, 197, 3), (3, 50, 2), (1, 256, 2), (2, 129, 1), (2, 16, 1)])
-def test_packed_attention(b, t, h):
+def _attention_oracle(q, k, v, keep=None, keep_prob=1.0):
+  """fp32 softmax attention; ``keep`` (B, H, Tq, Tk) drops attention weights after the softmax."""
+  d = q.shape[-1]
+  logits = torch.einsum("bqhd,bkhd->bhqk", q, k) / math.sqrt(d)
+  probs = torch.softmax(logits, -1)
+  if keep is not None:
+    probs = probs * keep / keep_prob
+  return torch.einsum("bhqk,bkhd->bqhd", probs, v)
+
+
+@pytest.mark.parametrize("b,t,h,d", [(2, 197, 3, 64), (3, 50, 2, 64), (1, 256, 2, 64),
+                                     (2, 129, 1, 64), (2, 16, 1, 64), (2, 257, 2, 80),
+                                     (1, 577, 2, 64), (2, 300, 1, 64), (2, 197, 2, 32),
+                                     (1, 300, 1, 80)])
+@pytest.mark.parametrize("general", ["0", "1"])
+def test_packed_attention(b, t, h, d, general, monkeypatch):
+  """Forward and packed gradient against fp32 PyTorch: the training shapes (197 and 50 tokens),
+  ViT-H/14 (257 tokens, head dim 80), 384-pixel fine-tuning (577 tokens: three key blocks with
+  rescaling in the forward pass, dQ accumulated outside TMEM in the backward pass). Head dim 64
+  with up to 256 tokens normally runs on the one-shot kernels; ``general`` = 1 sends it through
+  the key-blocked kernels as well."""
   from vmoe_b200.ops import attention_ops
+  monkeypatch.setenv("VMOE_B200_ATTN_GENERAL", general)
   torch.manual_seed(0)
-  qkv = torch.randn(b, t, 3, h, 64, device=DEV).bfloat16().requires_grad_()
+  qkv = torch.randn(b, t, 3, h, d, device=DEV).bfloat16().requires_grad_()
   out = attention_ops.packed_attention(qkv)
   dout = torch.randn_like(out)
   out.backward(dout)
   ref_in = qkv.detach().float().requires_grad_()
-  q, k, v = ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2]
-  logits = torch.einsum("bqhd,bkhd->bhqk", q, k) / 8.0
-  ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(logits, -1), v)
+  ref = _attention_oracle(ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2])
   ref.backward(dout.float())
   _close(out, ref, 2e-2)
   _close(qkv.grad[:, :, 2], ref_in.grad[:, :, 2], 3e-2)  # dV
   _close(qkv.grad[:, :, 1], ref_in.grad[:, :, 1], 3e-2)  # dK
   _close(qkv.grad[:, :, 0], ref_in.grad[:, :, 0], 3e-2)  # dQ
+
+
+@pytest.mark.parametrize("b,t,h,d", [(40, 257, 4, 80), (40, 577, 4, 64), (160, 197, 2, 32)])
+def test_attention_ctas_that_process_several_work_items(b, t, h, d):
+  """More (batch, head, query tile) items than resident CTAs: every persistent CTA runs its
+  barriers through several items (and key blocks). The first and the last batch entries are
+  compared with fp32 PyTorch; no bounded wait may have run out."""
+  from vmoe_b200.ops import attention_ops
+  torch.manual_seed(0)
+  qkv = torch.randn(b, t, 3, h, d, device=DEV).bfloat16().requires_grad_()
+  out = attention_ops.packed_attention(qkv)
+  dout = torch.randn_like(out)
+  out.backward(dout)
+  assert int(attention_ops.status_word(DEV).item()) == 0
+  for sl in (slice(0, 2), slice(b - 2, b)):
+    ref_in = qkv.detach()[sl].float().requires_grad_()
+    ref = _attention_oracle(ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2])
+    ref.backward(dout[sl].float())
+    _close(out[sl], ref, 2e-2)
+    _close(qkv.grad[sl], ref_in.grad, 3e-2)
+
+
+@pytest.mark.parametrize("b,t,h,d,p", [(2, 197, 2, 64, 0.1), (1, 300, 1, 80, 0.25)])
+def test_packed_attention_dropout_with_the_kernels_mask(b, t, h, d, p):
+  """Dropout of the attention weights: the kernels' keep mask is a hash that
+  ``dropout_keep_mask`` restates in PyTorch, so forward and backward can be checked exactly."""
+  from vmoe_b200.ops import attention_ops
+  torch.manual_seed(1)
+  seed = 0x1234_5678_9ABC
+  qkv = torch.randn(b, t, 3, h, d, device=DEV).bfloat16().requires_grad_()
+  out = attention_ops.packed_attention(qkv, p, seed)
+  dout = torch.randn_like(out)
+  out.backward(dout)
+  keep = attention_ops.dropout_keep_mask(seed, b, h, t, t, p, device=DEV)
+  keep_prob = attention_ops.dropout_keep_quantum(p) / 256.0
+  assert abs(float(keep.float().mean()) - keep_prob) < 0.01
+  ref_in = qkv.detach().float().requires_grad_()
+  ref = _attention_oracle(ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2], keep.float(), keep_prob)
+  ref.backward(dout.float())
+  _close(out, ref, 2e-2)
+  for i in range(3):
+    _close(qkv.grad[:, :, i], ref_in.grad[:, :, i], 3e-2)
+
+
+@pytest.mark.parametrize("b,tq,tk,h,d", [(3, 1, 196, 4, 64), (2, 150, 70, 2, 64), (2, 5, 257, 2, 80)])
+def test_cross_attention_with_separate_query_and_key_value_tensors(b, tq, tk, h, d):
+  """The pooling head's case: a probe (one query) over the tokens, keys and values sliced out
+  of one packed projection; and general Tq != Tk."""
+  from vmoe_b200.ops import attention_ops
+  torch.manual_seed(2)
+  q = torch.randn(b, tq, h, d, device=DEV).bfloat16().requires_grad_()
+  kv = torch.randn(b, tk, 2, h, d, device=DEV).bfloat16().requires_grad_()
+  out = attention_ops.attention(q, kv[:, :, 0], kv[:, :, 1])
+  dout = torch.randn_like(out)
+  out.backward(dout)
+  qf, kvf = q.detach().float().requires_grad_(), kv.detach().float().requires_grad_()
+  ref = _attention_oracle(qf, kvf[:, :, 0], kvf[:, :, 1])
+  ref.backward(dout.float())
+  _close(out, ref, 2e-2)
+  _close(q.grad, qf.grad, 3e-2)
+  _close(kv.grad, kvf.grad, 3e-2)
 
 
 @pytest.mark.parametrize("g,s,e,k,noisy", [(4, 197, 8, 2, True), (3, 50, 8, 1, False),

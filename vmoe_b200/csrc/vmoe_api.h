@@ -195,9 +195,13 @@ VMOE_API int vmoe_optimizer_step(float* p, const float* g, float* m, float* v, v
                                  vmoe_stream_t stream);
 
 // ----------------------------------------------------------------------------- attention
-// Non-causal softmax attention, head dim 64, 1 <= T <= 256, bf16. q/k/v/dq/dk/dv and
-// out/d_out are addressed as ptr + b*batch + t*tok + h*head (+ d), strides in elements and
-// multiples of 8, so q, k and v may point into one packed (B, T, 3, H, 64) projection output.
+// Non-causal softmax attention, bf16, head dim D a multiple of 16 up to 80, T queries and Tk keys
+// (keys and values of one head must fit shared memory: vmoe_attention_supported). q, k, v, dq, dk,
+// dv and out / d_out are addressed as ptr + b*batch + t*tok + h*head (+ d), strides in elements
+// and multiples of 8, so q, k and v may point into one packed (B, T, 3, H, D) projection, or q
+// into one tensor and k, v into another (cross-attention: Tk and the kv_* / gkv_* strides).
+// dropout_p > 0 drops attention weights with a keep mask that is a hash of (seed, batch, head,
+// query, key); the backward pass must get the same dropout_p and seed.
 typedef struct VmoeAttnArgs {
   const void* q;
   const void* k;
@@ -210,11 +214,19 @@ typedef struct VmoeAttnArgs {
   void* dv;
   unsigned* status;
   int64_t B, H, T, D;
-  int64_t q_tok, q_head, q_batch;  // strides of q, k and v
+  int64_t q_tok, q_head, q_batch;  // strides of q (and of k, v unless kv_* are set)
   int64_t o_tok, o_head, o_batch;  // strides of out and d_out
-  int64_t g_tok, g_head, g_batch;  // strides of dq, dk and dv
+  int64_t g_tok, g_head, g_batch;  // strides of dq (and of dk, dv unless gkv_* are set)
   float scale;                     // usually 1 / sqrt(D)
+  float dropout_p;                 // 0: no dropout
+  int64_t Tk;                      // keys (0: same as T)
+  int64_t kv_tok, kv_head, kv_batch;     // strides of k and v (all 0: the q strides)
+  int64_t gkv_tok, gkv_head, gkv_batch;  // strides of dk and dv (all 0: the dq strides)
+  uint64_t seed;                   // dropout seed
+  float* dq_acc;  // backward, when vmoe_attention_bwd_needs_dq_acc: fp32 zeros, B*T*H*D
 } VmoeAttnArgs;
+VMOE_API int32_t vmoe_attention_supported(int64_t tq, int64_t tk, int64_t d);
+VMOE_API int32_t vmoe_attention_bwd_needs_dq_acc(int64_t tq, int64_t d);
 VMOE_API int vmoe_attention_fwd(const VmoeAttnArgs* args, vmoe_stream_t stream);
 VMOE_API int vmoe_attention_bwd(const VmoeAttnArgs* args, vmoe_stream_t stream);
 

@@ -244,19 +244,17 @@ class MultiHeadDotProductAttention(nn.Module):
       if self.query_ln is None:
         a = ops.attention_packed(qkv, dropout_p=self.dropout_rate, training=self.training)
         return self.out(a.reshape(b, tq, h * d), residual=residual)
-      if not (self.training and self.dropout_rate > 0):
-        # QK-norm: normalise the query and key slices, re-pack and use the fused kernel.
-        from vmoe_b200.ops import norm as norm_ops
-        if (ops.cuda_kernels_enabled() and norm_ops.qk_norm_packed_supported(
-            qkv, self.query_ln.scale, self.key_ln.scale, self.query_ln.bias, self.key_ln.bias)):
-          packed = norm_ops.qk_norm_packed(qkv, self.query_ln.scale, self.key_ln.scale,
-                                           self.query_ln.eps)
-        else:
-          qn, kn = self.query_ln(qkv[:, :, 0]), self.key_ln(qkv[:, :, 1])
-          packed = torch.stack([qn, kn, qkv[:, :, 2]], dim=2)
-        a = ops.attention_packed(packed)
-        return self.out(a.reshape(b, tq, h * d), residual=residual)
-      q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+      # QK-norm: normalise the query and key slices, re-pack and use the fused kernel.
+      from vmoe_b200.ops import norm as norm_ops
+      if (ops.cuda_kernels_enabled() and norm_ops.qk_norm_packed_supported(
+          qkv, self.query_ln.scale, self.key_ln.scale, self.query_ln.bias, self.key_ln.bias)):
+        packed = norm_ops.qk_norm_packed(qkv, self.query_ln.scale, self.key_ln.scale,
+                                         self.query_ln.eps)
+      else:
+        qn, kn = self.query_ln(qkv[:, :, 0]), self.key_ln(qkv[:, :, 1])
+        packed = torch.stack([qn, kn, qkv[:, :, 2]], dim=2)
+      a = ops.attention_packed(packed, dropout_p=self.dropout_rate, training=self.training)
+      return self.out(a.reshape(b, tq, h * d), residual=residual)
     else:
       w, bias = self.qkv.weight, self.qkv.bias
       q = ops.linear(inputs_q, w[:hdim], bias[:hdim]).reshape(b, tq, h, d)

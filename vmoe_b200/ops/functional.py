@@ -264,20 +264,31 @@ def layer_norm_fork(x: torch.Tensor, weight: Optional[torch.Tensor],
 # ----------------------------------------------------------------------------------- attention
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               dropout_p: float = 0.0, training: bool = False) -> torch.Tensor:
-  """Non-causal softmax attention; ``q: (B, Tq, heads, d)``, ``k, v: (B, Tk, heads, d)``."""
+  """Non-causal softmax attention; ``q: (B, Tq, heads, d)``, ``k, v: (B, Tk, heads, d)``.
+
+  bf16 CUDA tensors of a shape the fused kernels cover run on them (dropout of the attention
+  weights included); everything else is evaluated with PyTorch ops."""
+  p_drop = dropout_p if training else 0.0
+  if _fast(q) and k.dtype == q.dtype and v.dtype == q.dtype:
+    from vmoe_b200.ops import attention_ops
+    if attention_ops.separate_supported(q, k, v):
+      seed = attention_ops.new_seed() if p_drop > 0 else 0
+      return attention_ops.attention(q, k, v, p_drop, seed)
   d = q.shape[-1]
   scale = 1.0 / math.sqrt(d)
   logits = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
   probs = torch.softmax(logits.float(), dim=-1).to(q.dtype)
-  if training and dropout_p > 0:
-    probs = F.dropout(probs, dropout_p, True)
+  if p_drop > 0:
+    probs = F.dropout(probs, p_drop, True)
   return torch.einsum("bhqk,bkhd->bqhd", probs, v)
 
 
 def attention_packed(qkv: torch.Tensor, dropout_p: float = 0.0, training: bool = False):
   """Self-attention on the packed QKV projection ``(B, T, 3, H, D)`` -> ``(B, T, H, D)``."""
-  if _fast(qkv) and not (training and dropout_p > 0):
+  if _fast(qkv):
     from vmoe_b200.ops import attention_ops
     if attention_ops.packed_supported(qkv):
-      return attention_ops.packed_attention(qkv)
+      p_drop = dropout_p if training else 0.0
+      seed = attention_ops.new_seed() if p_drop > 0 else 0
+      return attention_ops.packed_attention(qkv, p_drop, seed)
   return attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], dropout_p, training)
