@@ -140,3 +140,72 @@ def test_saved_values_are_those_at_the_time_of_the_call(tmp_path, mesh):
   assert step == 1 and restored.model.head.bias.detach()[0].item() == 7.0
   assert float(restored.model.head.weight.detach().abs().sum()) >= 0.0
   assert any(float(p.detach().abs().sum()) > 0 for p in restored.model.parameters())
+
+
+def test_older_checkpoints_survive_a_failed_write(tmp_path, mesh, monkeypatch):
+  """keep_last = 1: the previous step is deleted only after the new one is completely on disk.
+  A write that fails leaves the previous step restorable."""
+  from vmoe_b200.checkpoints import partitioned
+  state = _state(mesh)
+  manager = trainer.CheckpointManager(workdir=str(tmp_path), every_steps=1, keep_last=1, mesh=mesh)
+  with torch.no_grad():
+    state.model.head.bias.fill_(1.0)
+  state.step = 1
+  manager.save(1, state, force=True)
+  manager.wait_until_finished()
+  assert manager.all_steps() == [1]
+
+  class _Failing:
+    def get(self, timeout=None):
+      raise IOError("disk full")
+
+  real_save = partitioned.save_checkpoint
+  monkeypatch.setattr(partitioned, "save_checkpoint", lambda *a, **k: _Failing())
+  state.step = 2
+  manager.save(2, state, force=True)
+  assert 1 in manager.all_steps()          # nothing is deleted while the write is in flight
+  with pytest.raises(IOError):
+    manager.wait_until_finished()
+  assert 1 in manager.all_steps()          # ... nor after it failed
+  monkeypatch.setattr(partitioned, "save_checkpoint", real_save)
+  other = _state(mesh, seed=3)
+  assert manager.restore(other) == 1
+  assert float(other.model.head.bias[0]) == 1.0
+  # A later successful save removes the old step once it has finished.
+  state.step = 3
+  manager.save(3, state, force=True)
+  assert 1 in manager.all_steps()
+  manager.wait_until_finished()
+  assert manager.all_steps() == [3]
+  manager.close()
+
+
+def test_adafactor_resumes_with_its_second_moments(tmp_path, mesh):
+  """k steps, save, restore into a fresh state, one more step == k + 1 uninterrupted steps."""
+  opt_cfg = {"name": "big_vision_adafactor", "learning_rate": 0.01, "momentum": 0.9}
+  def make(seed):
+    return trainer.create_train_state(model_config=MODEL, optimizer_config=opt_cfg,
+                                      total_steps=10, mesh=mesh, seed=seed, image_size=16)
+  loss_fn, _, _ = trainer.get_loss_fn("softmax_xent")
+  g = torch.Generator().manual_seed(0)
+  batches = [(torch.rand(4, 16, 16, 3, generator=g),
+              torch.nn.functional.one_hot(torch.randint(0, 5, (4,), generator=g), 5).float())
+             for _ in range(4)]
+  ref = make(0)
+  for x, y in batches[:3]:
+    trainer.train_step(ref, x, y, loss_fn)
+  torch.manual_seed(77)   # the router's noise comes from the global generator
+  trainer.train_step(ref, *batches[3], loss_fn)
+  run = make(0)
+  for x, y in batches[:3]:
+    trainer.train_step(run, x, y, loss_fn)
+  manager = trainer.CheckpointManager(workdir=str(tmp_path), every_steps=1, keep_last=1, mesh=mesh)
+  manager.save(3, run, force=True)
+  manager.wait_until_finished()
+  resumed = make(5)
+  assert manager.restore(resumed) == 3
+  manager.close()
+  torch.manual_seed(77)
+  trainer.train_step(resumed, *batches[3], loss_fn)
+  for (n, a), (_, b) in zip(ref.model.named_parameters(), resumed.model.named_parameters()):
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6, msg=n)

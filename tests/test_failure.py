@@ -66,3 +66,17 @@ def test_check_status_decodes_and_clears_the_word():
   assert "ready-flag wait" in str(e.value) and "peer signal wait" in str(e.value)
   assert int(status.item()) == 0
   failure.check_status(status)  # zero: nothing to report
+
+
+def test_store_barrier_can_reuse_a_name():
+  """The second barrier of a name must wait for second arrivals, not see the first ones."""
+  store = FakeStore()
+  failure._BARRIER_CALLS.clear()
+  # both ranks pass the first barrier (rank 1 arrives first, then rank 0 completes it)
+  with pytest.raises(failure.BarrierTimeout):
+    failure.store_barrier("epoch", timeout_s=0.02, store=store, rank=1, world_size=2, poll_s=0.01)
+  failure.store_barrier("epoch", timeout_s=0.1, store=store, rank=0, world_size=2)
+  # second use: only rank 0 arrives; the keys of the first use must not satisfy it
+  with pytest.raises(failure.BarrierTimeout) as e:
+    failure.store_barrier("epoch", timeout_s=0.05, store=store, rank=0, world_size=2, poll_s=0.01)
+  assert e.value.missing == [1]

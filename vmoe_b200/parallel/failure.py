@@ -104,15 +104,25 @@ class Heartbeat:
       time.sleep(poll_s)
 
 
+_BARRIER_CALLS: dict = {}
+
+
 def store_barrier(name: str, timeout_s: float = 60.0, store=None, rank: Optional[int] = None,
                   world_size: Optional[int] = None, poll_s: float = 0.02) -> None:
-  """Named barrier through the key-value store; ``BarrierTimeout`` lists who is missing."""
+  """Named barrier through the key-value store; ``BarrierTimeout`` lists who is missing.
+
+  A name may be used any number of times: every rank counts its own calls per (store, name)
+  and the count is part of the key, so the n-th barrier of a name only sees the n-th arrivals
+  (all ranks must call a given name equally often, as with any collective)."""
   store = store if store is not None else _default_store()
   rank = dist.get_rank() if rank is None else rank
   world = dist.get_world_size() if world_size is None else world_size
-  store.set(f"vmoe_b200/barrier/{name}/{rank}", "1")
+  gen_key = (id(store), name, rank)
+  gen = _BARRIER_CALLS.get(gen_key, 0)
+  _BARRIER_CALLS[gen_key] = gen + 1
+  store.set(f"vmoe_b200/barrier/{name}/{gen}/{rank}", "1")
   deadline = time.monotonic() + timeout_s
-  keys = [f"vmoe_b200/barrier/{name}/{r}" for r in range(world)]
+  keys = [f"vmoe_b200/barrier/{name}/{gen}/{r}" for r in range(world)]
   while True:
     missing: List[int] = [r for r, k in enumerate(keys) if not store.check([k])]
     if not missing:

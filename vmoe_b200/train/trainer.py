@@ -387,6 +387,7 @@ class CheckpointManager:
     self.mesh = mesh or mesh_lib.get_mesh()
     self.num_shards = num_shards
     self._pending = None
+    self._pending_step = None
     self._pool = ckpt_base.ThreadPool(8)
     if self.mesh.rank == 0:
       os.makedirs(self.dir, exist_ok=True)
@@ -405,9 +406,16 @@ class CheckpointManager:
     return max(steps) if steps else None
 
   def wait_until_finished(self):
+    """Waits for the save in flight. Older checkpoints are deleted only now, once the new one
+    is completely on disk on every rank: until then they are the only restorable state, and a
+    write that fails (the exception propagates from here) must leave them in place."""
     if self._pending is not None:
-      self._pending.get(self.wait_seconds)
-      self._pending = None
+      pending, step = self._pending, self._pending_step
+      self._pending = self._pending_step = None
+      pending.get(self.wait_seconds)
+      from vmoe_b200.parallel import multihost_utils
+      if multihost_utils.all_ranks_ok(True):
+        self._cleanup(step)
 
   def save(self, step: int, state: TrainState, force: bool = False, last_seen_index=None) -> bool:
     if not (force or self.should_save(step)):
@@ -421,7 +429,7 @@ class CheckpointManager:
     self._pending = partitioned.save_checkpoint(
         f"{self.prefix}_{step}", tree, shardings=specs, mesh=self.mesh,
         num_shards=self.num_shards, thread_pool=self._pool)
-    self._cleanup(step)
+    self._pending_step = step
     return True
 
   def _cleanup(self, current: int):
@@ -496,10 +504,40 @@ def train_state_to_tree(state: TrainState):
     if nu is not None:
       tree["opt_state"]["nu"] = nu
       spec_tree["opt_state"]["nu"] = specs
+    if opt.name == "big_vision_adafactor":
+      af, af_specs = _adafactor_to_tree(opt)
+      tree["opt_state"]["adafactor"] = af
+      spec_tree["opt_state"]["adafactor"] = af_specs
   if state.rngs:
     tree["rngs"] = {k: g.get_state().numpy() for k, g in state.rngs.items()}
     spec_tree["rngs"] = {k: None for k in state.rngs}
   return tree, spec_tree
+
+
+def _adafactor_to_tree(opt):
+  """Second-moment accumulators of big_vision Adafactor (``v`` or the factored ``v_row`` /
+  ``v_col``), keyed by the parameter's path, in this package's own array layout. Accumulators
+  of expert-sharded parameters that keep the leading expert axis are saved as local blocks."""
+  from vmoe_b200.utils.misc import unflatten_dict
+  flat, specs = {}, {}
+  for b in opt.buckets.values():
+    for key, p in b.entries:
+      for name, v in opt.af_state[id(p)].items():
+        flat[f"{key}/{name}"] = v.detach().cpu().numpy().copy()
+        keeps_expert_axis = v.dim() >= 1 and p.dim() >= 1 and v.shape[0] == p.shape[0] and (
+            name == "v" or _adafactor_keeps_axis0(opt, p, name))
+        specs[f"{key}/{name}"] = ("expert",) if (getattr(p, "expert_sharded", False) and
+                                                 keeps_expert_axis) else None
+  return unflatten_dict(flat, sep="/"), unflatten_dict(specs, sep="/")
+
+
+def _adafactor_keeps_axis0(opt, p, name: str) -> bool:
+  from vmoe_b200.train.optimizer import _factored_dims
+  dims = _factored_dims(p.shape, opt.af["min_dim_size_to_factor"])
+  if dims is None:
+    return True
+  d1, d0 = dims
+  return (d0 if name == "v_row" else d1) != 0
 
 
 def _moments_to_flax(state, opt):
@@ -549,6 +587,20 @@ def load_train_state_from_tree(state: TrainState, tree) -> None:
         for b in opt.buckets.values():
           for _, p in b.entries:
             p.data = saved[id(p)]
+    if opt.name == "big_vision_adafactor" and "adafactor" in st:
+      from vmoe_b200.utils.misc import flatten_dict
+      flat = flatten_dict(st["adafactor"], sep="/")
+      for b in opt.buckets.values():
+        for key, p in b.entries:
+          for name, v in opt.af_state[id(p)].items():
+            if f"{key}/{name}" in flat:
+              src = torch.as_tensor(np.asarray(flat[f"{key}/{name}"]))
+              if (src.shape != v.shape and getattr(p, "expert_sharded", False) and
+                  state.mesh is not None and src.dim() >= 1 and v.dim() >= 1 and
+                  src.shape[0] == v.shape[0] * state.mesh.num_partitions):
+                el = v.shape[0]   # a full array: keep this rank's experts
+                src = src[state.mesh.expert_rank * el:(state.mesh.expert_rank + 1) * el]
+              v.copy_(src.to(device=v.device, dtype=v.dtype))
   if opt is not None:
     opt.sync_shadows()
   if state.rngs and "rngs" in tree:
@@ -733,6 +785,14 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
       batches(), size=int(config.dataset.train.get("prefetch_device", 2) or 2), device=device)
 
   status_every = int(config.get("check_device_status_every_steps", 100) or 100)
+  # Optional host-side failure detection (``config.heartbeat = {every_steps, timeout_seconds}``).
+  heartbeat = None
+  hb_cfg = config.get("heartbeat")
+  if hb_cfg and mesh.world_size > 1:
+    from vmoe_b200.parallel import failure
+    heartbeat = failure.Heartbeat()
+    heartbeat_every = int(hb_cfg.get("every_steps", 1) or 1)
+    heartbeat_timeout = float(hb_cfg.get("timeout_seconds", 60.0))
   multihost_utils.sync_devices("training:start")
   if init_step == 0 and ckpt_cfg.get("every_steps"):
     ckpt_manager.save(0, state, force=True)
@@ -760,7 +820,15 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
     progress_hook(step, scalar_metrics={**train_cost_fn(step),
                                         "train": {k: v for k, v in metrics.items()
                                                   if not isinstance(v, Mapping)}})
-    if step % status_every == 0:
+    if heartbeat is not None:
+      # Every rank publishes the step it reached; a rank that stopped or left is named here, on
+      # the host, before this rank launches kernels that would wait for it.
+      heartbeat.beat(step)
+      if step % heartbeat_every == 0:
+        heartbeat.check(step, timeout_s=heartbeat_timeout)
+    if step % status_every == 0 or ckpt_manager.should_save(step):
+      # Also before every save: a bounded wait that ran out means this step applied gradients
+      # or expert rows that were incomplete, and such a state must not become a restore point.
       check_device_status(state)
     with progress_hook.timed("ckpt", wait_jax_async_dispatch=False):
       ckpt_manager.save(step, state)
@@ -769,6 +837,7 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
       fewshot_hook(step)
   ckpt_manager.wait_until_finished()
   if ckpt_cfg.get("every_steps") and train_steps > init_step and ckpt_manager.latest_step() != train_steps:
+    check_device_status(state)
     ckpt_manager.save(train_steps, state, force=True)
     ckpt_manager.wait_until_finished()
   ckpt_manager.close()
