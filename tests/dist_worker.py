@@ -135,7 +135,8 @@ def main():
   loss_fn, _, _ = trainer.get_loss_fn("softmax_xent")
   _, metrics = trainer.train_step(state, images[rank * per:(rank + 1) * per],
                                   labels[rank * per:(rank + 1) * per], loss_fn)
-  out = {"main_loss": float(metrics["main_loss"]), "grad_norm": float(metrics["global_norm/grads"])}
+  out = {"main_loss": float(metrics["main_loss"]), "grad_norm": float(metrics["global_norm/grads"]),
+         "aux_loss": float(metrics.get("auxiliary_loss", 0.0))}
   # Save and reload the sharded checkpoint, then compare against the live state.
   mgr = trainer.CheckpointManager(workdir=outdir, every_steps=1, mesh=mesh)
   mgr.save(1, state, force=True)

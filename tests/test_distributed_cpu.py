@@ -57,7 +57,11 @@ def test_two_ranks_expert_parallel_step_and_checkpoint(tmp_path):
   # as one process (groups never span ranks, so routing is identical).
   for key in ("expert_kernel_sum", "head_sum", "q_sum", "grad_norm"):
     assert abs(two[0][key] - one[key]) <= 2e-4 * abs(one[key]) + 1e-5, (key, two[0][key], one[key])
-  assert abs((two[0]["main_loss"] + two[1]["main_loss"]) / 2 - one["main_loss"]) < 1e-4
+  # Logged metrics are means over the global batch on every rank (they travel in the
+  # optimizer's single small all-reduce), not the rank's local means.
+  for r in two:
+    assert abs(r["main_loss"] - one["main_loss"]) < 1e-4, (r["main_loss"], one["main_loss"])
+    assert abs(r["aux_loss"] - one["aux_loss"]) < 1e-4, (r["aux_loss"], one["aux_loss"])
   files = sorted(os.listdir(d2 / "ckpt"))
   assert files == ["ckpt_1.data-00000-of-00002", "ckpt_1.data-00001-of-00002", "ckpt_1.index"]
 

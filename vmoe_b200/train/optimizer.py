@@ -177,6 +177,7 @@ class Optimizer:
       b.set_meta(wd_fn, frozen_fn, gs_fn)
     self.last_learning_rate = float(self.lr_schedule(0))
     self.last_norms: Dict[str, torch.Tensor] = {}
+    self.last_extra: Optional[torch.Tensor] = None
     if name == "big_vision_adafactor":
       self._init_adafactor()
 
@@ -191,25 +192,49 @@ class Optimizer:
       for _, p in b.entries:
         yield p
 
-  def _combine_sums(self, index: int) -> torch.Tensor:
-    """Global sum (over buckets and expert shards) of ``sums[index]`` as a device scalar."""
-    total = None
-    for kind, b in self.buckets.items():
-      v = b.sums[index]
-      if (kind == "expert" and self.mesh is not None and self.mesh.num_partitions > 1 and
-          dist.is_initialized()):
-        v = v.clone()
-        dist.all_reduce(v, group=self.mesh.expert_group)
-      total = v if total is None else total + v
-    return total
+  def _sharded(self) -> bool:
+    """Expert parameters are spread over several ranks: their sums need a reduction."""
+    return ("expert" in self.buckets and self.mesh is not None and
+            self.mesh.num_partitions > 1 and dist.is_initialized())
+
+  @staticmethod
+  def _reduce_sum(vec: torch.Tensor, group) -> torch.Tensor:
+    """The one small all-reduce of this module (sum over ``group``, in place)."""
+    dist.all_reduce(vec, group=group)
+    return vec
+
+  def _finish_sums(self, sums: torch.Tensor, extra: Optional[torch.Tensor]):
+    """Global values of the per-bucket sums of squares and of the caller's scalars.
+
+    ``sums``: double (3,) sums of this rank's expert bucket (zeros without one). ``extra``:
+    1-D tensor of per-rank scalars to be averaged over all ranks (train metrics). Everything
+    travels in ONE all-reduce over the world: expert sums come back multiplied by the number
+    of replicas of each shard, the scalars by the world size, and both are divided out here.
+    """
+    world = dist.get_world_size() if (dist.is_initialized() and self.mesh is not None
+                                      and self.mesh.world_size > 1) else 1
+    if world == 1:
+      return sums, extra
+    parts = [sums.double()] + ([extra.double().reshape(-1)] if extra is not None else [])
+    if not self._sharded() and extra is None:
+      return sums, extra
+    vec = self._reduce_sum(torch.cat(parts), self.mesh.world_group)
+    out_sums = sums
+    if self._sharded():
+      out_sums = vec[:3] / float(self.mesh.num_replicas)
+    out_extra = None if extra is None else (vec[3:] / world).to(extra.dtype).reshape(extra.shape)
+    return out_sums, out_extra
 
   # ------------------------------------------------------------------ step
   @torch.no_grad()
-  def step(self, grad_div: float = 1.0) -> Dict[str, torch.Tensor]:
+  def step(self, grad_div: float = 1.0,
+           extra: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
     """Applies one update. Gradients are first divided by ``grad_div``.
 
     Returns global L2 norms of gradients (after division and gradient scale, before
-    clipping), updates and new parameters as 0-dim tensors.
+    clipping), updates and new parameters as 0-dim tensors. ``extra`` (1-D tensor of per-rank
+    scalars, e.g. the step's metrics) is averaged over all ranks in the same small all-reduce
+    that completes the norms; the result is left in ``self.last_extra``.
     """
     lr = float(self.lr_schedule(self.step_count))
     self.last_learning_rate = lr
@@ -217,18 +242,42 @@ class Optimizer:
     for b in self.buckets.values():
       b.rebind_grads()
       b.sums.zero_()
+    dev = next(iter(self.buckets.values())).device
+    zeros3 = torch.zeros(3, dtype=torch.float64, device=dev)
     if self.name == "big_vision_adafactor":
-      norms = self._adafactor_step(lr, grad_div)
+      dense_sums, expert_sums = self._adafactor_step(lr, grad_div)
+      expert_sums, self.last_extra = self._finish_sums(expert_sums, extra)
+      tot = dense_sums + expert_sums
+      norms = {"grads": torch.sqrt(tot[0]), "updates": torch.sqrt(tot[1]),
+               "params": torch.sqrt(tot[2])}
     else:
       for b in self.buckets.values():
         self._sumsq(b)
-      g2 = self._combine_sums(0)
+      dense = self.buckets.get("dense")
+      expert = self.buckets.get("expert")
+      dense_g2 = dense.sums[0].clone() if dense is not None else zeros3[0]
+      expert_g2 = expert.sums[0].clone() if expert is not None else zeros3[0]
+      if self.clip_norm > 0 and self._sharded():
+        # Clipping needs the global gradient norm before the update: the expert shards' part is
+        # summed over the expert group now; everything else waits for the end of the step.
+        expert_g2 = self._reduce_sum(expert_g2.reshape(1), self.mesh.expert_group)[0]
+        expert_g2_done = True
+      else:
+        expert_g2_done = False
+      g2 = dense_g2 + expert_g2   # exact when reduced or unsharded; only read when clipping
       for b in self.buckets.values():
         b.sums[0] = g2
         self._update(b, lr, t, grad_div)
-      norms = {"grads": torch.sqrt(g2) / grad_div,
-               "updates": torch.sqrt(self._combine_sums(1)),
-               "params": torch.sqrt(self._combine_sums(2))}
+      esums = zeros3.clone()
+      if expert is not None:
+        esums = torch.stack([expert_g2 if not expert_g2_done else zeros3[0], expert.sums[1],
+                             expert.sums[2]])
+      esums, self.last_extra = self._finish_sums(esums, extra)
+      dsums = dense.sums if dense is not None else zeros3
+      total_g2 = dense_g2 + (expert_g2 if expert_g2_done else esums[0])
+      norms = {"grads": torch.sqrt(total_g2) / grad_div,
+               "updates": torch.sqrt(dsums[1] + esums[1]),
+               "params": torch.sqrt(dsums[2] + esums[2])}
     for b in self.buckets.values():
       for _, p in b.entries:
         if b.shadow is not None:
@@ -315,25 +364,26 @@ class Optimizer:
     step = self.step_count
     tt = float(step - af["decay_offset"]) + 1.0
     decay = min(af["decay_rate_max"], 1.0 - tt ** (-af["decay_rate"]))
-    g2 = torch.zeros((), dtype=torch.float64, device=next(iter(self.buckets.values())).device)
+    dev = next(iter(self.buckets.values())).device
+    g2_parts = {"dense": torch.zeros((), dtype=torch.float64, device=dev),
+                "expert": torch.zeros((), dtype=torch.float64, device=dev)}
     scaled = []
-    for b in self.buckets.values():
+    for kind, b in self.buckets.items():
       for i, (key, p) in enumerate(b.entries):
         g = b.view_of(b.grads, i) * (float(b.meta[b.offsets[i] // CHUNK, 2]) / grad_div)
         scaled.append(g)
-        part = (g.double() ** 2).sum()
-        if (getattr(p, "expert_sharded", False) and self.mesh is not None and
-            self.mesh.num_partitions > 1 and dist.is_initialized()):
-          dist.all_reduce(part, group=self.mesh.expert_group)
-        g2 += part
-    gnorm = torch.sqrt(g2)
+        g2_parts[kind] += (g.double() ** 2).sum()
     fac = 1.0
     if self.clip_norm > 0:
-      fac = self.clip_norm / max(float(gnorm), self.clip_norm)
-    upd2 = torch.zeros_like(g2)
-    par2 = torch.zeros_like(g2)
+      eg2 = g2_parts["expert"]
+      if self._sharded():
+        eg2 = self._reduce_sum(eg2.clone().reshape(1), self.mesh.expert_group)[0]
+      gnorm = torch.sqrt(g2_parts["dense"] + eg2)
+      fac = self.clip_norm / torch.clamp(gnorm, min=self.clip_norm)   # stays on the device
+    upd2 = {k: torch.zeros_like(v) for k, v in g2_parts.items()}
+    par2 = {k: torch.zeros_like(v) for k, v in g2_parts.items()}
     it = iter(scaled)
-    for b in self.buckets.values():
+    for kind, b in self.buckets.items():
       for i, (key, p) in enumerate(b.entries):
         g = next(it) * fac
         if self.clip_value > 0:
@@ -363,9 +413,10 @@ class Optimizer:
         sh = getattr(p, "_bf16_shadow", None)
         if sh is not None:
           sh.copy_(p.data)
-        upd2 += (upd.double() ** 2).sum()
-        par2 += (p.data.double() ** 2).sum()
-    return {"grads": gnorm, "updates": torch.sqrt(upd2), "params": torch.sqrt(par2)}
+        upd2[kind] += (upd.double() ** 2).sum()
+        par2[kind] += (p.data.double() ** 2).sum()
+    pack = lambda k: torch.stack([g2_parts[k], upd2[k], par2[k]])
+    return pack("dense"), pack("expert")
 
   # ------------------------------------------------------------------ state
   def state_dict(self) -> Dict[str, Any]:

@@ -26,11 +26,15 @@ class TrainState:
   rngs: Optional[Dict[str, torch.Generator]] = None
   mesh: Optional[mesh_lib.Mesh] = None
 
-  def apply_gradients_and_compute_global_norms(self, microsteps: int = 1):
-    """All-reduces the accumulated gradients, applies the optimizer and bumps the step."""
+  def apply_gradients_and_compute_global_norms(self, microsteps: int = 1,
+                                               extra: Optional[torch.Tensor] = None):
+    """All-reduces the accumulated gradients, applies the optimizer and bumps the step.
+
+    ``extra``: per-rank scalars (1-D tensor) to average over all ranks together with the norm
+    reduction; the averages are left in ``self.optimizer.last_extra``."""
     mesh = self.mesh or mesh_lib.get_mesh()
     reduce_lib.reduce_gradients(self.optimizer, mesh)
-    norms = self.optimizer.step(grad_div=float(mesh.world_size * max(1, microsteps)))
+    norms = self.optimizer.step(grad_div=float(mesh.world_size * max(1, microsteps)), extra=extra)
     self.step += 1
     return norms
 

@@ -131,7 +131,21 @@ def train_step(state: TrainState, images: Tensor, labels: Tensor,
     grads_for_summary = {key: p.grad.detach().clone() / n for key, _, p in
                          naming.named_flax_parameters(state.model, prefix="")
                          if p.grad is not None}
-  norms = state.apply_gradients_and_compute_global_norms(microsteps=n)
+  # The metrics are means over this rank's examples; the logged values are means over the global
+  # batch (``vmoe/train/trainer.py:663-666``). They ride in the optimizer's one small
+  # all-reduce instead of getting collectives of their own.
+  flat_metrics = misc.flatten_dict(metrics, sep="\x00")
+  keys = [k for k, v in flat_metrics.items() if isinstance(v, torch.Tensor) and v.dim() == 0
+          and v.is_floating_point()]
+  mesh = state.mesh or mesh_lib.get_mesh()
+  extra = None
+  if keys and mesh is not None and mesh.world_size > 1:
+    extra = torch.stack([flat_metrics[k].detach().float() for k in keys])
+  norms = state.apply_gradients_and_compute_global_norms(microsteps=n, extra=extra)
+  if extra is not None and state.optimizer.last_extra is not None:
+    for k, v in zip(keys, state.optimizer.last_extra.unbind(0)):
+      flat_metrics[k] = v
+    metrics = misc.unflatten_dict(flat_metrics, sep="\x00")
   metrics.update({f"global_norm/{k}": v for k, v in norms.items()})
   if summarizer is not None:
     flat = misc.flatten_dict(state.state_dict(), sep="/")
