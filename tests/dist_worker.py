@@ -123,6 +123,38 @@ def main():
     dist.barrier()
     dist.destroy_process_group()
     return
+  if mode == "contrastive":
+    # Two-tower SigLIP step: 8 (image, text) pairs split over the ranks; dense towers so that
+    # the only thing the split can change is which texts each image is contrasted with.
+    from vmoe_b200.projects.contrastive import trainer as ctrainer
+    enc = {"num_layers": 1, "mlp_dim": 32, "num_heads": 2, "dropout_rate": 0.0,
+           "attention_dropout_rate": 0.0, "moe": {"layers": ()}}
+    image = {"num_classes": 12, "patch_size": (8, 8), "hidden_size": 16, "classifier": "token",
+             "representation_size": None, "encoder": dict(enc)}
+    text = {"vocab_size": 50, "num_classes": 12, "hidden_size": 16, "encoder": dict(enc)}
+    state = ctrainer.create_train_state(
+        model_config={"image": image, "text": text, "scale_init": 10.0, "bias_init": -10.0},
+        optimizer_config=dict(name="sgd", learning_rate=0.1), total_steps=10, mesh=mesh, seed=0,
+        image_size=16)
+    gen = torch.Generator().manual_seed(5)
+    images = torch.rand(8, 16, 16, 3, generator=gen)
+    texts = torch.randint(1, 50, (8, 16), generator=gen)
+    per = 8 // world
+    sl = slice(rank * per, (rank + 1) * per)
+    before = {n: p.detach().clone() for n, p in state.model.named_parameters()}
+    _, metrics = ctrainer.train_step(state, images[sl], texts[sl], ctrainer.sigmoid_loss)
+    delta = {n: float((p.detach() - before[n]).double().abs().sum())
+             for n, p in state.model.named_parameters()}
+    out = {"main_loss": float(metrics["main_loss"]),
+           "grad_norm": float(metrics["global_norm/grads"]),
+           "delta_txt": sum(v for n, v in delta.items() if n.startswith("txt.")),
+           "delta_img": sum(v for n, v in delta.items() if n.startswith("img.")),
+           "scale": float(state.model.s.detach()), "bias": float(state.model.b.detach())}
+    json.dump(out, open(os.path.join(outdir, f"r{rank}.json"), "w"))
+    if dist.is_initialized():
+      dist.barrier()
+      dist.destroy_process_group()
+    return
   multihost_utils.sync_devices("start")
   state = trainer.create_train_state(
       model_config=small_config(),

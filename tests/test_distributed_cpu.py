@@ -102,3 +102,15 @@ def test_checkpoint_read_failure_on_one_rank_moves_all_ranks_to_the_previous_ste
     assert r["restored"] == 1 and r["step"] == 1 and r["bias"] == 1.0
   assert "injected read failure" in r1["explicit"]
   assert "on another rank" in r0["explicit"]
+
+
+def test_contrastive_loss_is_taken_over_the_global_batch(tmp_path):
+  """Two ranks with 4 pairs each must produce the loss, gradient norm and update of one process
+  with all 8 pairs: every image is contrasted with the texts of the whole global batch."""
+  d1, d2 = tmp_path / "w1", tmp_path / "w2"
+  d1.mkdir(); d2.mkdir()
+  one = _launch(1, "contrastive", d1, partitions=1)[0]
+  two = _launch(2, "contrastive", d2, partitions=1)
+  for r in two:
+    for key in ("main_loss", "grad_norm", "delta_txt", "delta_img", "scale", "bias"):
+      assert abs(r[key] - one[key]) <= 1e-4 * abs(one[key]) + 1e-6, (key, r[key], one[key])

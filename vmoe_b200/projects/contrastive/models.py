@@ -99,6 +99,18 @@ class TwoTower(nn.Module):
     kwargs.update(extra)
     return cls(*args, deterministic=deterministic, mesh=mesh, **kwargs)
 
+  def embed_pair(self, images: torch.Tensor, texts: torch.Tensor):
+    """``(zimg, ztxt, scale, bias, metrics)``: the normalised embeddings of both towers and the
+    logit scale / bias, for losses that build their own logits (global-batch contrast)."""
+    zimg, mi = self.img(images)
+    ztxt, mt = self.txt(texts)
+    zimg, ztxt = zimg.float(), ztxt.float()
+    zimg = zimg / (zimg.norm(dim=-1, keepdim=True) + 1e-8)
+    ztxt = ztxt / (ztxt.norm(dim=-1, keepdim=True) + 1e-8)
+    self.last_embeddings["zimg"], self.last_embeddings["ztxt"] = zimg.detach(), ztxt.detach()
+    s = torch.exp(self.s)
+    return zimg, ztxt, s, self.b, {"img": mi, "txt": mt, "scale": s.detach()}
+
   def forward(self, images: Optional[torch.Tensor], texts: Optional[torch.Tensor]):
     if images is None and texts is None:
       raise ValueError("You must give at least one of images or texts arrays.")
