@@ -51,8 +51,8 @@ def get_base_config() -> ConfigDict:
   config.save_checkpoint.keep_last = 1
   config.save_checkpoint.wait_seconds = 300
   config.report_progress = ConfigDict(type_safe=False)
-  config.report_progress.every_secs = None
-  config.report_progress.every_steps = 100
+  config.report_progress.every_secs = 60.0
+  config.report_progress.every_steps = 250
   config.evaluate = ConfigDict(type_safe=False)
   config.evaluate.every_steps = 1_000
   config.profile = ConfigDict()

@@ -1,5 +1,6 @@
 """Fine-tuning config ``vmoe_b16_imagenet21k_randaug_strong_ft_cifar10`` of the V-MoE paper
-(``vmoe/configs/vmoe_paper/vmoe_b16_imagenet21k_randaug_strong_ft_cifar10.py``); the settings live in ``finetune.py``."""
+(``vmoe/configs/vmoe_paper/vmoe_b16_imagenet21k_randaug_strong_ft_cifar10.py``); the values live in
+``finetune.py`` under the variant ``b16_cifar10``."""
 from vmoe_b200.configs.vmoe_paper import finetune
 
 
@@ -7,5 +8,4 @@ def get_config():
   return finetune.get_config("b16_cifar10")
 
 
-def get_hyper(hyper):
-  return finetune.get_hyper(hyper) if hasattr(finetune, "get_hyper") else hyper.product([])
+get_hyper = finetune.get_hyper

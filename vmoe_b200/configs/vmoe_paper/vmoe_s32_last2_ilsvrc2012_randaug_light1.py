@@ -41,10 +41,21 @@ def get_config(arg: str = "") -> ConfigDict:
   if not synthetic:
     config.dataset.test = get_data_params_eval("imagenet2012", "validation")
     config.dataset.imagenet_v2 = get_data_params_eval("imagenet_v2", "test")
+    config.dataset.imagenet_real = common.get_data_config(
+        name="imagenet2012_real", split="validation", shuffle_buffer=None, batch_size=BATCH_SIZE,
+        cache="batched",
+        process=("decode|resize_small(256)|central_crop(224)|value_range(-1,1)|"
+                 f'onehot({NUM_CLASSES}, inkey="real_label", outkey="labels")|'
+                 'keep("image", "labels")'))
   config.loss = ConfigDict({"name": "sigmoid_xent"})
   config.description = "ViT-S/32, E=8, K=2, Last 2, 300 Epochs"
   config.model = common.get_vmoe_config(config.description, 224, NUM_CLASSES)
+  config.model.encoder.moe.dropout_rate = 0.2
   config.optimizer = common.get_optimizer_config(config.description)
+  # Different from the standard values of the paper's ImageNet-21k runs.
+  config.optimizer.weight_decay = [(".*/kernel", 0.1)]
+  config.optimizer.learning_rate.peak_value = 3e-3
+  config.optimizer.gradient_clip.global_norm = 1.0
   config.train_epochs = common.get_num_epochs(config.description)
   config.mixup = common.get_mixup_config("light1")
   config.num_expert_partitions = config.model.encoder.moe.num_experts

@@ -11,13 +11,51 @@ from vmoe_b200.utils.config_dict import ConfigDict
 get_fewshot_config = common_fewshot.get_fewshot
 
 
-def get_optimizer_rsqrt_config() -> ConfigDict:
+def get_adam_config() -> ConfigDict:
   return ConfigDict({
       "name": "adam", "b1": 0.9, "b2": 0.999, "mu_dtype": "float32",
       "weight_decay": (("head/kernel", 3.0), (".*/kernel", 0.03)),
       "gradient_clip": {"global_norm": 1.0},
-      "learning_rate": {"schedule": "big_vision_rsqrt", "peak_value": 1e-3,
-                        "warmup_steps": 10_000, "cooldown_steps": 50_000, "timescale": 100_000},
+  }, type_safe=False)
+
+
+def get_optimizer_linear_config() -> ConfigDict:
+  """Adam with linear decay, as in "Scaling Vision Transformers"."""
+  config = get_adam_config()
+  config.learning_rate = ConfigDict({"schedule": "warmup_linear_decay", "peak_value": 8e-4,
+                                     "end_value": 0.0, "warmup_steps": 10_000}, type_safe=False)
+  return config
+
+
+def get_optimizer_rsqrt_config() -> ConfigDict:
+  """Adam with the reciprocal-square-root schedule of the ViT-22B paper."""
+  config = get_adam_config()
+  config.learning_rate = ConfigDict({
+      "schedule": "big_vision_rsqrt", "peak_value": 1e-3, "warmup_steps": 10_000,
+      "cooldown_steps": 50_000, "timescale": 10_000}, type_safe=False)
+  return config
+
+
+def get_imagenet_config(batch_size: int, resize_hi: int = 256, resize_lo: int = 224,
+                        randaug: str = "", data_dir: Optional[str] = None) -> ConfigDict:
+  """Dataset variants for training / evaluating on ImageNet: train, val, test, v2, real."""
+  randaug = f"|{randaug}" if randaug and randaug[0] != "|" else randaug
+  pp_common = lambda inkey: (f'value_range(-1,1)|onehot(1000, inkey="{inkey}", outkey="labels")|'
+                             'keep("image", "labels")')
+  pp_train = f'decode_jpeg_and_inception_crop({resize_lo})|flip_lr{randaug}|{pp_common("label")}'
+  pp_eval1 = f'decode|resize_small({resize_hi})|central_crop({resize_lo})|{pp_common("label")}'
+  pp_eval2 = (f'decode|resize_small({resize_hi})|central_crop({resize_lo})|'
+              f'ignore_no_labels(labels_key="real_label")|{pp_common("real_label")}')
+  ev = lambda name, split, pp: {"name": name, "split": split, "process": pp,
+                                "batch_size": batch_size, "data_dir": data_dir, "cache": "batched"}
+  return ConfigDict({
+      "train": {"name": "imagenet2012", "split": "train[:99%]", "process": pp_train,
+                "batch_size": batch_size, "data_dir": data_dir, "cache": "loaded",
+                "shuffle_buffer": 250_000},
+      "val": ev("imagenet2012", "train[99%:]", pp_eval1),
+      "test": ev("imagenet2012", "validation", pp_eval1),
+      "v2": ev("imagenet_v2", "test", pp_eval1),
+      "real": ev("imagenet2012_real", "validation", pp_eval2),
   }, type_safe=False)
 
 
