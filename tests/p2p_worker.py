@@ -84,6 +84,57 @@ def oracle(tensors, k, c, rank, world):
           W2.grad[es], B2.grad[es]]
 
 
+def run_soft(exchange, tensors, e, c, steps=2):
+  """Soft-MoE-style layer: real-valued dispatch / combine weights over every (expert, slot),
+  slot rows exchanged over peer memory inside the expert GEMMs."""
+  os.environ["VMOE_B200_P2P"] = "1"
+  x0, wd0, wc0, w1, b1, w2, b2, dy = tensors
+  mlp = Mlp()
+  mlp.w1, mlp.b1, mlp.w2, mlp.b2 = [t.detach().clone().requires_grad_() for t in (w1, b1, w2, b2)]
+  outs = []
+  for _ in range(steps):
+    x = x0.detach().clone().requires_grad_()
+    wd = wd0.detach().clone().requires_grad_()
+    wc = wc0.detach().clone().requires_grad_()
+    for p in (mlp.w1, mlp.b1, mlp.w2, mlp.b2):
+      p.grad = None
+    disp = moe_core.Bfloat16Dispatcher(moe_core.EinsumDispatcher(
+        combine_weights=wc, dispatch_weights=wd, exchange=exchange))
+    y = disp.apply_experts(mlp, x)
+    y.backward(dy)
+    outs = [y.detach(), x.grad, wd.grad, wc.grad, mlp.w1.grad, mlp.b1.grad, mlp.w2.grad,
+            mlp.b2.grad]
+  torch.cuda.synchronize()
+  return outs
+
+
+def oracle_soft(tensors, rank, world):
+  """fp32 einsum formulation over the global batch (weights rounded to bf16 like the kernels')."""
+  x0, wd0, wc0, w1, b1, w2, b2, dy0 = tensors
+  g = x0.shape[0]
+  X = _gather(x0, world).float().requires_grad_()
+  WD = _gather(wd0, world).float().requires_grad_()
+  WC = _gather(wc0, world).float().requires_grad_()
+  DY = _gather(dy0, world).float()
+  W1 = _gather(w1, world).float().requires_grad_()
+  B1 = _gather(b1, world).float().requires_grad_()
+  W2 = _gather(w2, world).float().requires_grad_()
+  B2 = _gather(b2, world).float().requires_grad_()
+  G, S, E, C = WD.shape
+  q = lambda t: t + (t.detach().bfloat16().float() - t.detach())   # bf16 value, fp32 gradient
+  xs = torch.einsum("gsec,gsh->egch", q(WD), X).reshape(E, G * C, -1)
+  hid = torch.nn.functional.gelu(torch.baddbmm(B1.unsqueeze(1), xs, W1.transpose(1, 2)),
+                                 approximate="tanh")
+  ye = torch.baddbmm(B2.unsqueeze(1), hid, W2.transpose(1, 2)).reshape(E, G, C, -1)
+  Y = torch.einsum("gsec,egch->gsh", q(WC), ye)
+  Y.backward(DY)
+  el = w1.shape[0]
+  sl = slice(rank * g, (rank + 1) * g)
+  es = slice(rank * el, (rank + 1) * el)
+  return [Y.detach()[sl], X.grad[sl], WD.grad[sl], WC.grad[sl], W1.grad[es], B1.grad[es],
+          W2.grad[es], B2.grad[es]]
+
+
 def rel_errs(got, ref):
   errs = []
   for a, b in zip(got, ref):
@@ -128,8 +179,28 @@ def main():
     if name != "b16_layer":
       ref = run(ex, False, tensors, k, c)
       results[name] = rel_errs(got, ref)
+  # Soft-MoE-style layers: (groups, tokens, hidden, mlp, experts, slots per expert)
+  for name, (g, s, h, m, e, c) in {"soft_c1": (32, 49, 64, 128, 4 * world, 1),
+                                     "soft_c2": (16, 40, 128, 256, 2 * world, 2)}.items():
+    torch.manual_seed(200 + rank)
+    el = e // world
+    x = torch.randn(g, s, h, device=dev).bfloat16()
+    logits = torch.randn(g, s, e, c, device=dev)
+    wd = torch.softmax(logits, dim=1)
+    wc = torch.softmax(logits.reshape(g, s, e * c), dim=-1).reshape(g, s, e, c)
+    dy = torch.randn(g, s, h, device=dev).bfloat16()
+    w1 = torch.randn(el, m, h, device=dev) * 0.05
+    b1 = torch.randn(el, m, device=dev) * 0.1
+    w2 = torch.randn(el, h, m, device=dev) * 0.05
+    b2 = torch.randn(el, h, device=dev) * 0.1
+    got = run_soft(ex, (x, wd, wc, w1, b1, w2, b2, dy), e, c)
+    want = oracle_soft((x, wd, wc, w1.bfloat16().float(), b1, w2.bfloat16().float(), b2, dy),
+                       rank, world)
+    oracle_errs[name] = rel_errs(got, want)
+  soft_comms = sum(1 for k in moe_ops._LAYER_COMMS)
   status = [int(cm.status.item()) for cm in moe_ops._LAYER_COMMS.values()]
-  json.dump({"errs": results, "oracle_errs": oracle_errs, "status": status},
+  json.dump({"errs": results, "oracle_errs": oracle_errs, "status": status,
+             "layer_comms": soft_comms},
             open(os.path.join(outdir, f"p2p_r{rank}.json"), "w"))
   dist.barrier()
   dist.destroy_process_group()

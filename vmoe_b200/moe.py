@@ -165,6 +165,26 @@ class EinsumDispatcher(BaseDispatcher):
       out = torch.einsum("gsn,gnh->gsh", w2.to(flat.dtype), flat)
     return out.reshape(g, s, *x.shape[3:])
 
+  def apply_experts(self, mlp, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
+    """Dispatch, experts, combine in one call. When the experts are spread over several GPUs
+    with peer memory, the slot rows travel inside the expert GEMMs (``ops/moe_dense_p2p.py``)
+    instead of through two all-to-alls; otherwise this is ``sparse_moe_apply``."""
+    g, s, e, c = self.combine_weights.shape
+    out = None
+    if x.is_cuda and x.dim() == 3:
+      from vmoe_b200.ops import moe_dense_p2p
+      w_d = self._dispatch_w().reshape(g, s, e * c)
+      w_c = self.combine_weights.reshape(g, s, e * c)
+      if (moe_dense_p2p.applicable(self.exchange, mlp, g, e, c, x) and
+          _einsum_ops().supported(w_c, x)):
+        ops_ = _einsum_ops()
+        xs = ops_.dispatch(w_d if w_d.is_floating_point() else w_d.to(x.dtype), x)
+        ys = moe_dense_p2p.expert_exchange_and_mlp(mlp, self.exchange, xs, e, c)
+        out = ops_.combine(w_c, ys)
+    if out is None:
+      out = sparse_moe_apply(mlp, self, x)
+    return out if residual is None else out + residual
+
 
 @dataclasses.dataclass
 class ExpertIndicesDispatcher(BaseDispatcher):
@@ -230,6 +250,13 @@ class Bfloat16Dispatcher(BaseDispatcher):
     if data.is_floating_point():
       data = data.to(torch.bfloat16)
     return self.dispatcher.combine(data).to(dtype)
+
+  def apply_experts(self, mlp, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
+    inner = getattr(self.dispatcher, "apply_experts", None)
+    if inner is not None and x.dtype == torch.bfloat16:
+      return inner(mlp, x, residual=residual)  # the payload already is bf16
+    out = sparse_moe_apply(mlp, self, x)
+    return out if residual is None else out + residual
 
 
 # --------------------------------------------------------------------------------- routing
