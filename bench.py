@@ -16,8 +16,9 @@ random-init weights. Two numbers are measured over the same K steps each:
   step, the host->device copy of that step's images and labels from pinned host memory and a
   device->host read of the step's loss.
 
-Rank 0 prints one JSON line. ``--impl reference`` would time the unmodified reference
-(JAX/Flax); it is not installable offline here, so that arm prints an ``unavailable`` line.
+Rank 0 prints one JSON line. ``--impl reference`` times the unmodified reference (JAX / Flax,
+``baseline/run_reference.py``) when its dependencies are installed and prints an ``unavailable``
+line otherwise.
 """
 from __future__ import annotations
 
@@ -41,6 +42,8 @@ def parse_args():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="vmoe_b200", choices=["vmoe_b200", "reference"])
   ap.add_argument("--per-gpu-batch", type=int, default=PER_GPU_BATCH)
+  ap.add_argument("--global-batch", type=int, default=None,
+                  help="total images per step over all GPUs (overrides --per-gpu-batch)")
   ap.add_argument("--model", default=MODEL_DESC)
   ap.add_argument("--library-ops", action="store_true",
                   help="run PyTorch library ops instead of the package's kernels (stand-in baseline)")
@@ -55,22 +58,52 @@ def parse_args():
 
 
 def reference_arm(args) -> int:
-  """The reference needs jax, flax, optax, clu, tensorflow, tfds, ml_collections and chex;
-  none of them is installed or present in the offline wheelhouse, and the tree has no
-  setup.py / pyproject.toml to install from."""
-  why = None
+  """Runs the unmodified reference tree under ``baseline/_ref`` through its own training step
+  (``baseline/run_reference.py``) when its dependencies (jax, flax, optax, ml_collections ...)
+  can be imported; otherwise prints the ``unavailable`` line. Rank 0 only: JAX drives all local
+  GPUs from one process."""
+  rank = int(os.environ.get("RANK", "0"))
+  if rank != 0:
+    return 0
+  here = os.path.dirname(os.path.abspath(__file__))
+  for p in (os.path.join(here, "baseline", "_ref"), here):
+    if p not in sys.path:
+      sys.path.insert(0, p)
   try:
-    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
     import jax  # noqa: F401
     import flax  # noqa: F401
+    import optax  # noqa: F401
     import vmoe  # noqa: F401
-    why = "reference importable but no runner is wired up"
+    from baseline import run_reference
   except Exception as e:  # pylint: disable=broad-except
-    why = (f"reference not installable offline: {type(e).__name__}: {e}; jax/flax/optax/clu/"
-           "tensorflow are absent from the image and the wheelhouse, and the reference tree has no "
-           "setup.py or pyproject.toml")
-  if int(os.environ.get("RANK", "0")) == 0:
+    why = (f"the reference's dependencies are not installed: {type(e).__name__}: {e} "
+           "(it needs jax, flax, optax, clu, ml_collections; none can be installed offline)")
     print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
+    return 0
+  try:
+    res = run_reference.run(gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                            per_gpu_batch=args.per_gpu_batch, description=args.model,
+                            num_classes=NUM_CLASSES, image_size=IMAGE_SIZE)
+  except Exception as e:  # pylint: disable=broad-except
+    print(json.dumps({"impl": "reference",
+                      "unavailable": f"the reference's step failed: {type(e).__name__}: {e}"
+                      .replace("\n", " ")}))
+    return 0
+  out = {
+      "metric": "V-MoE B/16 train images/s", "value": res["value"], "unit": "images/s",
+      "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+      "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16",
+      "data": "synthetic images uniform[-1,1] 224x224x3, 21843-way multi-hot labels; random-init weights",
+      "impl": "reference",
+      "config": {"model": "V-MoE B/16, 8 experts every odd block, K=2, capacity 1.05, BPR, "
+                          "sigmoid xent, Adam wd 0.1",
+                 "global_batch": res["global_batch"], "seq_len": 197,
+                 "parallelism": f"dp{args.gpus} x ep{res['num_partitions']}",
+                 "timing": "host clock around block_until_ready (JAX has no CUDA events)"},
+      "e2e": res["e2e"], "final_loss": res["final_loss"],
+  }
+  print(json.dumps(out))
   return 0
 
 
@@ -151,6 +184,10 @@ def main() -> int:
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   if world != args.gpus:
     raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N>1")
+  if args.global_batch is not None:
+    if args.global_batch % world:
+      raise SystemExit(f"--global-batch {args.global_batch} is not divisible by {world} GPUs")
+    args.per_gpu_batch = args.global_batch // world
   device = torch.device("cuda", local_rank)
   torch.cuda.set_device(device)
   if not args.library_ops:

@@ -72,3 +72,47 @@ def test_bench_help_lists_the_contract_flags():
   assert out.returncode == 0
   for flag in ("--gpus", "--steps", "--warmup", "--impl", "--mode", "--ensemble-size"):
     assert flag in out.stdout
+
+
+def test_reference_arm_plumbing_with_fake_modules(monkeypatch, capsys):
+  """``bench.py --impl reference``: without JAX it prints the ``unavailable`` line; with the
+  reference's dependencies importable (faked here) it hands the benchmark's arguments to
+  ``baseline/run_reference.py`` and prints the benchmark's JSON schema with its result."""
+  import importlib
+  import json
+  import sys as _sys
+  import types
+  _sys.path.insert(0, ROOT)
+  bench = importlib.import_module("bench")
+  args = types.SimpleNamespace(gpus=2, steps=7, warmup=3, per_gpu_batch=64, model=bench.MODEL_DESC)
+  monkeypatch.delenv("RANK", raising=False)
+  for name in ("jax", "flax", "optax"):
+    monkeypatch.setitem(_sys.modules, name, None)     # import raises ImportError
+  assert bench.reference_arm(args) == 0
+  line = json.loads(capsys.readouterr().out.strip())
+  assert line["impl"] == "reference" and "not installed" in line["unavailable"]
+
+  for name in ("jax", "flax", "optax", "vmoe"):
+    monkeypatch.setitem(_sys.modules, name, types.ModuleType(name))
+  seen = {}
+
+  def fake_run(**kw):
+    seen.update(kw)
+    return {"ms_per_step": 50.0, "value": kw["per_gpu_batch"] * kw["gpus"] / 0.05,
+            "final_loss": 1.0, "global_batch": kw["per_gpu_batch"] * kw["gpus"],
+            "num_partitions": 2,
+            "e2e": {"value": 2000.0, "unit": "images/s", "ms_per_step": 64.0,
+                    "h2d_bytes_per_step": 123, "d2h_bytes_per_step": 4, "last_loss": 1.0}}
+
+  from baseline import run_reference
+  monkeypatch.setattr(run_reference, "run", fake_run)
+  assert bench.reference_arm(args) == 0
+  line = json.loads(capsys.readouterr().out.strip())
+  assert seen == dict(gpus=2, steps=7, warmup=3, per_gpu_batch=64, description=bench.MODEL_DESC,
+                      num_classes=21843, image_size=224)
+  assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["steps"] == 7
+  assert line["value"] == 2560.0 and line["e2e"]["h2d_bytes_per_step"] == 123
+  assert line["config"]["global_batch"] == 128 and line["metric"] == "V-MoE B/16 train images/s"
+  # other ranks stay silent: JAX drives every local GPU from one process
+  monkeypatch.setenv("RANK", "1")
+  assert bench.reference_arm(args) == 0 and capsys.readouterr().out == ""
