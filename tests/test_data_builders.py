@@ -78,3 +78,46 @@ def test_get_datasets_builds_one_iterator_per_variant():
   assert len(valid) == 3
   flags = np.concatenate([np.asarray(b["__valid__"]) for b in valid])
   assert flags.tolist() == [True] * 5 + [False]
+
+
+def _write_image_folder(root, splits):
+  from PIL import Image
+  rng = np.random.default_rng(0)
+  for split, per_class in splits.items():
+    for cls, n in per_class.items():
+      d = root / split / cls
+      d.mkdir(parents=True)
+      for i in range(n):
+        arr = rng.integers(0, 256, (20 + i, 24, 3), dtype=np.uint8)
+        Image.fromarray(arr).save(d / f"img_{i}.png")
+      (d / "notes.txt").write_text("not an image")
+
+
+def test_image_folder_builder_labels_splits_and_pipeline(tmp_path):
+  """Files under <root>/<split>/<class>/ with classes numbered alphabetically over all splits;
+  decoded and batched by the ordinary process string; the last batch is padded with invalid
+  examples."""
+  from vmoe_b200.data import builder as builder_lib
+  from vmoe_b200.data import input_pipeline
+  _write_image_folder(tmp_path, {"train": {"cat": 3, "dog": 2, "emu": 1},
+                                 "validation": {"cat": 2, "dog": 1}})
+  b = builder_lib.get_dataset_builder(name="folder", split="train", data_dir=str(tmp_path))
+  assert b.num_examples == 6 and b.num_classes == 3
+  ex = list(b.as_dataset())
+  assert [int(e["label"]) for e in ex] == [0, 0, 0, 1, 1, 2]
+  assert isinstance(ex[0]["image"], bytes) and ex[0]["file_name"].endswith("img_0.png")
+  assert builder_lib.get_dataset_builder(name="folder", split="train[50%:]",
+                                         data_dir=str(tmp_path)).num_examples == 3
+  ds = input_pipeline.get_dataset(
+      variant="val", name="folder", split="validation", batch_size=2, data_dir=str(tmp_path),
+      process='decode|resize(16)|value_range(-1,1)|onehot(3, inkey="label", outkey="labels")|'
+              'keep("image", "labels")')
+  batches = list(ds)
+  assert len(batches) == 2
+  assert batches[0]["image"].shape == (2, 16, 16, 3) and batches[0]["labels"].shape == (2, 3)
+  valid = np.concatenate([np.asarray(b_[input_pipeline.VALID_KEY]) for b_ in batches])
+  assert valid.tolist() == [True, True, True, False]
+  labels = np.concatenate([np.asarray(b_["labels"]) for b_ in batches])[:3].argmax(-1)
+  assert labels.tolist() == [0, 0, 1]
+  with pytest.raises(FileNotFoundError):
+    builder_lib.get_dataset_builder(name="folder", split="test", data_dir=str(tmp_path)).num_examples

@@ -4,8 +4,9 @@
 ``as_dataset`` = an iterable of example dicts for this process, ``get_num_fake_examples``).
 Builders: ``SyntheticBuilder`` (random images and labels of a named shape — used for
 benchmarks and tests, no files needed), ``ArrayBuilder`` (in-memory arrays or an ``.npz``
-file) and ``TfdsBuilder`` (TensorFlow Datasets, available only where ``tensorflow_datasets``
-is installed). Splits accept the TFDS slicing syntax (``'train[:99%]'``, ``'validation[100:]'``)
+file), ``ImageFolderBuilder`` (encoded image files in one directory per class, the usual
+on-disk form of ImageNet-like datasets) and ``TfdsBuilder`` (TensorFlow Datasets, available
+only where ``tensorflow_datasets`` is installed). Splits accept the TFDS slicing syntax (``'train[:99%]'``, ``'validation[100:]'``)
 and every process reads an even, contiguous sub-split of the examples (reference:
 ``vmoe/data/builder.py:31-133``).
 """
@@ -172,6 +173,90 @@ class ArrayBuilder(DatasetBuilder):
       yield {k: v[i] for k, v in arrays.items()}
 
 
+_IMAGE_EXTENSIONS = (".jpg", ".jpeg", ".png", ".bmp", ".gif", ".webp", ".ppm", ".tif", ".tiff")
+
+
+@dataclasses.dataclass
+class ImageFolderBuilder(DatasetBuilder):
+  """Image files on disk: ``<data_dir>/<split name>/<class name>/<file>``.
+
+  Class names sorted alphabetically give the integer labels (the same classes for every
+  split: they are taken from the union of the splits' sub-directories). Examples are
+  ``{"image": encoded bytes, "label": int64, "file_name": str}``: decoding, cropping and label
+  encoding are left to the ``process`` string (``decode|resize(...)|onehot(...)``), as with
+  TFDS sources. Every process reads an even, contiguous share of the (sorted, optionally
+  shuffled) file list of the split slice.
+  """
+  name: str = "folder"
+  split: str = "train"
+  data_dir: Optional[str] = None
+  manual_dir: Optional[str] = None     # accepted for config compatibility; unused
+  shuffle_files: bool = False
+  shuffle_seed: Optional[int] = None
+  _files: Optional[list] = dataclasses.field(default=None, repr=False)
+
+  def _class_names(self):
+    import os
+    root = self.data_dir
+    names = set()
+    for split_dir in sorted(os.listdir(root)):
+      p = os.path.join(root, split_dir)
+      if os.path.isdir(p):
+        names.update(d for d in os.listdir(p) if os.path.isdir(os.path.join(p, d)))
+    return sorted(names)
+
+  def _scan(self):
+    import os
+    if self._files is not None:
+      return self._files
+    if not self.data_dir or not os.path.isdir(self.data_dir):
+      raise FileNotFoundError(
+          f"ImageFolderBuilder: data_dir={self.data_dir!r} is not a directory; expected "
+          "<data_dir>/<split>/<class>/<image files>")
+    split_name = _SPLIT_RE.match(self.split.strip()).group("name")
+    split_dir = os.path.join(self.data_dir, split_name)
+    if not os.path.isdir(split_dir):
+      raise FileNotFoundError(f"ImageFolderBuilder: no directory {split_dir!r} for split "
+                              f"{self.split!r}")
+    label_of = {c: i for i, c in enumerate(self._class_names())}
+    files = []
+    for cls in sorted(os.listdir(split_dir)):
+      cdir = os.path.join(split_dir, cls)
+      if not os.path.isdir(cdir):
+        continue
+      for f in sorted(os.listdir(cdir)):
+        if f.lower().endswith(_IMAGE_EXTENSIONS):
+          files.append((os.path.join(cdir, f), label_of[cls]))
+    self._files = files
+    return files
+
+  @property
+  def num_classes(self) -> int:
+    return len(self._class_names())
+
+  def _split_size(self) -> int:
+    return len(self._scan())
+
+  @property
+  def num_examples(self) -> int:
+    _, start, stop = parse_split(self.split, self._split_size())
+    return stop - start
+
+  def as_dataset(self) -> Iterator[Dict[str, Any]]:
+    files = self._scan()
+    idx, cnt = _process_index_count()
+    _, start, stop = parse_split(self.split, len(files))
+    lo, hi = even_split(start, stop, idx, cnt)
+    order = np.arange(lo, hi)
+    if self.shuffle_files:
+      np.random.default_rng(self.shuffle_seed).shuffle(order)
+    for i in order:
+      path, label = files[int(i)]
+      with open(path, "rb") as f:
+        data = f.read()
+      yield {"image": data, "label": np.int64(label), "file_name": path}
+
+
 @dataclasses.dataclass
 class TfdsBuilder(DatasetBuilder):
   """TensorFlow Datasets source (images are left encoded; decode in the pipeline)."""
@@ -211,8 +296,9 @@ class TfdsBuilder(DatasetBuilder):
     except ImportError as e:
       raise ImportError(
           f"dataset {self.name!r} is read through tensorflow_datasets, which is not installed; "
-          "use name='synthetic' (random images / labels of the configured shape) or "
-          "name='arrays' (NumPy .npz files), e.g. --config.dataset.<variant>.name=synthetic"
+          "use name='folder' with data_dir=<root>/<split>/<class>/<image files>, "
+          "name='arrays' (NumPy .npz files) or name='synthetic' (random images / labels of the "
+          "configured shape), e.g. --config.dataset.<variant>.name=synthetic"
       ) from e
     split = tfds.split_for_jax_process(self.split, drop_remainder=False)
     data = self._builder().as_dataset(
@@ -224,9 +310,12 @@ class TfdsBuilder(DatasetBuilder):
 
 
 def get_dataset_builder(*, name: str, **kwargs) -> DatasetBuilder:
-  """``'synthetic'`` / ``'synthetic:<anything>'``, ``'arrays'`` or a TFDS dataset name."""
+  """``'synthetic'`` / ``'synthetic:<anything>'``, ``'arrays'``, ``'folder'`` /
+  ``'folder:<anything>'`` (image files under ``data_dir``) or a TFDS dataset name."""
   if name.startswith("synthetic"):
     return SyntheticBuilder(name=name, **kwargs)
   if name == "arrays":
     return ArrayBuilder(name=name, **kwargs)
+  if name == "folder" or name.startswith("folder:"):
+    return ImageFolderBuilder(name=name, **kwargs)
   return TfdsBuilder(name=name, **kwargs)
