@@ -117,6 +117,68 @@ def test_fused_moe_layer_forward_backward():
   _close(b2.grad, b2r.grad, 3e-2)
 
 
+@pytest.mark.parametrize("g,s,e,c", [(3, 50, 4, 16), (2, 196, 8, 25), (2, 700, 16, 44), (1, 10, 2, 12)])
+def test_experts_choose_plan_matches_topk(g, s, e, c):
+  """Plan kernel against torch.topk over the items of every (group, expert)."""
+  from vmoe_b200.ops import moe_ops
+  torch.manual_seed(0)
+  gates = torch.softmax(torch.randn(g, s, e, device=DEV), -1)
+  slot, slot_pair = moe_ops.experts_choose_plan(gates, c)
+  cc = min(c, s)
+  top_idx = torch.topk(gates.transpose(1, 2), cc, dim=-1).indices          # (g, e, cc)
+  want_pair = top_idx * e + torch.arange(e, device=DEV).reshape(1, e, 1)
+  assert torch.equal(slot_pair[:, :, :cc].long(), want_pair)
+  if c > s:
+    assert bool((slot_pair[:, :, s:] == -1).all())
+  want_slot = torch.full((g, s, e), c, dtype=torch.long, device=DEV)
+  ranks = torch.arange(cc, device=DEV).reshape(1, 1, cc).expand(g, e, cc)
+  want_slot.scatter_(1, top_idx.transpose(1, 2), ranks.transpose(1, 2))
+  # items beyond the capacity keep their rank >= c in the kernel's table only as "not taken"
+  assert torch.equal(slot.long().clamp(max=c), want_slot)
+
+
+def test_experts_choose_layer_forward_backward():
+  """Experts-choose MoE layer on the kernels against the einsum formulation in fp32."""
+  from vmoe_b200.ops import moe_ops
+  torch.manual_seed(0)
+  g, s, h, m, e, c = 3, 64, 128, 256, 4, 20
+  x = torch.randn(g, s, h, device=DEV).bfloat16().requires_grad_()
+  logits = torch.randn(g, s, e, device=DEV).requires_grad_()
+  w1 = (torch.randn(e, m, h, device=DEV) * 0.05).requires_grad_()
+  b1 = (torch.randn(e, m, device=DEV) * 0.1).requires_grad_()
+  w2 = (torch.randn(e, h, m, device=DEV) * 0.05).requires_grad_()
+  b2 = (torch.randn(e, h, device=DEV) * 0.1).requires_grad_()
+
+  class Mlp:
+    training = False
+    dropout_rate = 0.0
+  mlp = Mlp()
+  mlp.w1, mlp.b1, mlp.w2, mlp.b2 = w1, b1, w2, b2
+  disp = moe_ops.FusedTopItemsDispatcher(torch.softmax(logits, -1), c)
+  y = disp.apply_experts(mlp, x)
+  dy = torch.randn_like(y)
+  y.backward(dy)
+  metrics = disp.metrics()
+
+  xr, lr, w1r, b1r, w2r, b2r = [t.detach().float().requires_grad_()
+                                for t in (x, logits, w1, b1, w2, b2)]
+  ref_disp, ref_metrics = moe_core.get_top_items_per_expert_dispatcher(
+      torch.softmax(lr, -1), name="einsum", capacity=c)
+  xe = ref_disp.dispatch(xr)
+  hid = F.gelu(torch.baddbmm(b1r.unsqueeze(1), xe, w1r.transpose(1, 2)), approximate="tanh")
+  yr = ref_disp.combine(torch.baddbmm(b2r.unsqueeze(1), hid, w2r.transpose(1, 2)))
+  yr.backward(dy.float())
+  _close(y, yr, 3e-2)
+  _close(x.grad, xr.grad, 3e-2)
+  _close(logits.grad, lr.grad, 5e-2)
+  _close(w1.grad, w1r.grad, 3e-2)
+  _close(b1.grad, b1r.grad, 3e-2)
+  _close(w2.grad, w2r.grad, 3e-2)
+  _close(b2.grad, b2r.grad, 3e-2)
+  for key, want in ref_metrics.items():
+    torch.testing.assert_close(metrics[key].float(), want.float(), rtol=1e-5, atol=1e-6)
+
+
 @pytest.mark.parametrize("kind", ["sigmoid", "softmax"])
 def test_xent(kind):
   from vmoe_b200.ops import losses

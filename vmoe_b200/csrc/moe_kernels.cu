@@ -372,3 +372,75 @@ extern "C" int vmoe_moe_combine_bwd(const void* dy, const int32_t* slot_pair, co
       static_cast<int>(e), static_cast<int>(c), static_cast<int>(k), static_cast<int>(h));
   return launch_status();
 }
+
+// ------------------------------------------------------------------ "experts choose" plan
+// Every expert takes its `capacity` best items of the group (vmoe/moe.py:655-694,
+// jax.lax.top_k over the items: larger gate first, lower item index first among equals).
+// One CTA per (group, expert): the expert's column of gates is sorted in shared memory with a
+// bitonic network on 64-bit keys (inverted gate bits, item index), then
+//   slot_pair[g, e, c] = item * E + e   for the c-th best item (c < capacity),
+//   slot[g, item, e]   = rank of the item in the expert's order, or `capacity` if not taken.
+// In the indices form of the Top-K layer this is "K = E choices per item, choice j = expert j",
+// so the row movers, the peer-memory exchange and the combine kernels are shared.
+namespace vmoe {
+constexpr int EC_MAX_ITEMS = 4096;
+
+__global__ void __launch_bounds__(256)
+experts_choose_plan_kernel(const float* __restrict__ gates, int* __restrict__ slot,
+                           int* __restrict__ slot_pair, int s, int e, int capacity, int padded) {
+  extern __shared__ unsigned long long ec_keys[];
+  const int g = blockIdx.x / e, ee = blockIdx.x % e;
+  const float* col = gates + (static_cast<long long>(g) * s) * e + ee;
+  for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+    unsigned long long key = ~0ull;  // padding sorts last
+    if (i < s) {
+      const unsigned bits = __float_as_uint(col[static_cast<long long>(i) * e]);
+      // gates are non-negative, so their bit patterns order like their values
+      key = (static_cast<unsigned long long>(0xFFFFFFFFu - bits) << 32) | static_cast<unsigned>(i);
+    }
+    ec_keys[i] = key;
+  }
+  __syncthreads();
+  for (int size = 2; size <= padded; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < (padded >> 1); t += blockDim.x) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool ascending = (lo & size) == 0;
+        const unsigned long long a = ec_keys[lo], b = ec_keys[hi];
+        if ((a > b) == ascending) {
+          ec_keys[lo] = b;
+          ec_keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int r = threadIdx.x; r < s; r += blockDim.x) {
+    const int item = static_cast<int>(ec_keys[r] & 0xFFFFFFFFu);
+    slot[(static_cast<long long>(g) * s + item) * e + ee] = r < capacity ? r : capacity;
+    if (r < capacity)
+      slot_pair[(static_cast<long long>(g) * e + ee) * capacity + r] = item * e + ee;
+  }
+  // capacity > s: the remaining buffer slots stay empty
+  for (int r = s + threadIdx.x; r < capacity; r += blockDim.x)
+    slot_pair[(static_cast<long long>(g) * e + ee) * capacity + r] = -1;
+}
+}  // namespace vmoe
+
+extern "C" int vmoe_experts_choose_plan(const float* gates, int32_t* slot_out, int32_t* slot_pair,
+                                        int64_t groups, int64_t s, int64_t e, int64_t capacity,
+                                        vmoe_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (groups * s * e == 0) return 0;
+  if (s > EC_MAX_ITEMS) {
+    set_error("%s (code %d)", "experts_choose_plan: at most 4096 items per group", 0);
+    return -1;
+  }
+  int padded = 2;
+  while (padded < s) padded <<= 1;
+  experts_choose_plan_kernel<<<static_cast<unsigned>(groups * e), 256, padded * 8, stream>>>(
+      gates, slot_out, slot_pair, static_cast<int>(s), static_cast<int>(e),
+      static_cast<int>(capacity), padded);
+  return launch_status();
+}

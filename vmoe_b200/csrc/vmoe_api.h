@@ -155,6 +155,14 @@ VMOE_API int vmoe_patchify(const void* img, int32_t img_is_bf16, void* out, int6
 VMOE_API int vmoe_routing_plan(const float* gates, int32_t* expert_out, int32_t* slot_out,
                                int32_t* slot_pair, int64_t groups, int64_t s, int64_t e, int64_t k,
                                int64_t capacity, int32_t batch_priority, vmoe_stream_t stream);
+// "Experts choose" plan from softmax gates (groups, s, e) fp32, s <= 4096: every expert takes
+// its `capacity` largest gates of each group (ties: lower item first). Outputs: slot
+// (groups, s, e) = rank of the item in expert e's order if < capacity, else capacity (not
+// taken); slot_pair (groups, e, capacity) = item * e_total + expert (-1: empty slot). These are
+// the Top-K tables with K = e choices per item, choice j = expert j.
+VMOE_API int vmoe_experts_choose_plan(const float* gates, int32_t* slot_out, int32_t* slot_pair,
+                                      int64_t groups, int64_t s, int64_t e, int64_t capacity,
+                                      vmoe_stream_t stream);
 // Buffer row (g, e, c) at expert_base[e] + (g*C + c)*h  <-  weight * x[g, item] (zeros if the
 // slot is empty). expert_base is a device array of e addresses (local or peer memory).
 VMOE_API int vmoe_moe_gather_rows(const void* x, const int32_t* slot_pair, const float* weight,

@@ -221,6 +221,19 @@ class NoisyTopItemsPerExpertRouter(_RouterBase):
     gates = torch.softmax(logits, dim=-1)
     kwargs = dict(self.dispatcher_kwargs)
     use_bf16 = kwargs.pop("bfloat16", False)
+    if (inputs.is_cuda and inputs.dtype == torch.bfloat16 and ops.cuda_kernels_enabled() and
+        kwargs.get("name", "einsum") in ("einsum", "indices")):
+      # GPU path: plan kernel + the indices-form layer shared with Top-K routing.
+      from vmoe_b200.ops import moe_ops
+      g, s, e = gates.shape
+      if s <= moe_ops.EXPERTS_CHOOSE_MAX_ITEMS:
+        capacity = moe._resolve_capacity(
+            kwargs.get("capacity"), kwargs.get("capacity_factor"), s, e,
+            kwargs.get("capacity_ceil_or_round", "ceil"), kwargs.get("capacity_multiple_of", 4))
+        d = moe_ops.FusedTopItemsDispatcher(gates, capacity, exchange=self.exchange)
+        metrics = d.metrics()
+        metrics["auxiliary_loss"] = torch.zeros(g, dtype=gates.dtype, device=gates.device)
+        return d, metrics
     d, metrics = moe.get_top_items_per_expert_dispatcher(gates, exchange=self.exchange, **kwargs)
     if use_bf16:
       d = moe.Bfloat16Dispatcher(d)

@@ -487,3 +487,64 @@ class FusedTopKDispatcher(moe_core.BaseDispatcher):
     return _FusedMoeFn.apply(x, self.combine_weights, mlp.w1, mlp.b1, mlp.w2, mlp.b2, residual,
                              self.expert, self.slot, self.slot_pair, self.capacity,
                              self.exchange)
+
+
+def experts_choose_plan(gates: torch.Tensor, capacity: int):
+  """Runs the experts-choose plan kernel on ``gates (G, S, E)`` fp32 (CUDA, S <= 4096).
+
+  Returns int32 ``slot (G, S, E)`` (rank of the item in the expert's order, ``capacity`` if the
+  expert did not take it) and ``slot_pair (G, E, C)`` (``item * E + expert``, -1 for empty)."""
+  assert gates.is_cuda and gates.dtype == torch.float32 and gates.dim() == 3
+  gates = gates.contiguous()
+  g, s, e = gates.shape
+  slot = torch.empty(g, s, e, dtype=torch.int32, device=gates.device)
+  slot_pair = torch.empty(g, e, capacity, dtype=torch.int32, device=gates.device)
+  rc = _lib.lib().vmoe_experts_choose_plan(
+      _vp(gates.data_ptr()), _vp(slot.data_ptr()), _vp(slot_pair.data_ptr()), _i64(g), _i64(s),
+      _i64(e), _i64(capacity), _vp(_lib.stream_ptr()))
+  _lib.check(rc, "vmoe_experts_choose_plan")
+  _lib.count_launch()
+  return slot, slot_pair
+
+
+EXPERTS_CHOOSE_MAX_ITEMS = 4096
+
+
+class FusedTopItemsDispatcher(FusedTopKDispatcher):
+  """"Experts choose" dispatcher (every expert takes its ``capacity`` best items of a group;
+  ``vmoe/moe.py:655-694``) on the kernels of the Top-K layer: in indices form it is "every item
+  has E choices, choice j is expert j, taken or not", so the plan kernel fills the same tables
+  and the row movers, the peer-memory exchange and the combine kernels are shared."""
+
+  def __init__(self, gates: torch.Tensor, capacity: int,
+               exchange: ExpertExchange = LOCAL_EXCHANGE):
+    self.gates = gates
+    self.capacity = capacity
+    self.num_experts = gates.shape[-1]
+    self.exchange = exchange
+    g, s, e = gates.shape
+    self.slot, self.slot_pair = experts_choose_plan(gates.detach().float(), capacity)
+    self.expert = torch.arange(e, dtype=torch.int32, device=gates.device).expand(g, s, e)
+    self.expert = self.expert.contiguous()
+    self.combine_weights = gates  # choice j of an item is weighted by its gate for expert j
+
+  def metrics(self) -> dict:
+    """Per-group monitoring values of the reference (``vmoe/moe.py:676-693``)."""
+    g, s, e = self.gates.shape
+    taken = self.slot < self.capacity                      # (G, S, E)
+    per_item = taken.sum(dim=-1).to(torch.int32)           # (G, S)
+    gates = self.gates.detach()
+    sel = torch.where(taken, gates, torch.full_like(gates, float("inf")))
+    sel_max = torch.where(taken, gates, torch.full_like(gates, float("-inf")))
+    out = {
+        "num_experts_per_item_min": per_item.min(dim=1).values,
+        "num_experts_per_item_max": per_item.max(dim=1).values,
+        "min_selected_gate": sel.amin(dim=(1, 2)),
+        "max_selected_gate": sel_max.amax(dim=(1, 2)),
+    }
+    import math
+    log2e = int(math.log2(e))
+    for t in [2 ** i for i in range(log2e + 1)] + [e]:
+      out[f"ratio_processed_items_by_at_least_{t}_experts"] = (
+          (per_item >= t).sum(dim=1).to(gates.dtype) / s)
+    return out
