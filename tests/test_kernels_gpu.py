@@ -226,6 +226,38 @@ def test_optimizer_kernel_matches_cpu(name, kw):
     _close(pg._bf16_shadow, pc.data, 1e-2)
 
 
+@pytest.mark.parametrize("clip", [None, {"global_norm": 0.5}])
+def test_adafactor_kernels_match_the_pytorch_formulation(clip):
+  """big_vision Adafactor on the table-driven kernels against the per-tensor PyTorch
+  formulation on CPU: factored 2-D tensors with either axis the larger, a batched (expert)
+  tensor factored over its last two axes, a small matrix and a vector with full second moments."""
+  from vmoe_b200.train.optimizer import create_optimizer
+  torch.manual_seed(0)
+  shapes = [(300, 70), (40, 129), (5,), (3, 64, 48), (8, 16), (1000,)]
+  ps_c = [torch.nn.Parameter(torch.randn(s)) for s in shapes]
+  ps_g = [torch.nn.Parameter(p.detach().clone().to(DEV)) for p in ps_c]
+  mk = lambda ps: create_optimizer(
+      [(f"params/p{i}/kernel", p) for i, p in enumerate(ps)], name="big_vision_adafactor",
+      total_steps=10, learning_rate=0.01, weight_decay=[("p0", 0.1), ("p3", 0.01)],
+      gradient_clip=clip, momentum=0.9)
+  oc, og = mk(ps_c), mk(ps_g)
+  assert og._adafactor_cuda_plan() is not None and oc._adafactor_cuda_plan() is None
+  for step in range(4):
+    oc.zero_grad(); og.zero_grad()
+    for pc, pg in zip(ps_c, ps_g):
+      gr = torch.randn(pc.shape)
+      pc.grad.add_(gr); pg.grad.add_(gr.to(DEV))
+    nc, ng = oc.step(grad_div=2.0), og.step(grad_div=2.0)
+    for key in nc:
+      assert abs(float(nc[key]) - float(ng[key])) < 1e-3 * (1 + abs(float(nc[key]))), key
+  for i, (pc, pg) in enumerate(zip(ps_c, ps_g)):
+    torch.testing.assert_close(pg.data.cpu(), pc.data, rtol=2e-4, atol=2e-5, msg=f"p{i}")
+    _close(pg._bf16_shadow, pc.data, 1e-2)
+    for name, v in oc.af_state[id(pc)].items():
+      torch.testing.assert_close(og.af_state[id(pg)][name].cpu(), v, rtol=2e-4, atol=1e-7,
+                                 msg=f"p{i}/{name}")
+
+
 def test_graft_smoke():
   import __graft_entry__
   __graft_entry__.smoke()

@@ -202,6 +202,36 @@ VMOE_API int vmoe_optimizer_step(float* p, const float* g, float* m, float* v, v
                                  float clip_norm, float clip_value, float grad_div, double* sums,
                                  vmoe_stream_t stream);
 
+// big_vision Adafactor over a table of tensors (device array of VmoeAdafactorTensor). A tensor
+// is (batch, rows, cols) row-major fp32 with its gradient, momentum and optional bf16 shadow;
+// `factored` tensors keep the moving averages of the row means (vr: batch x rows) and column
+// means (vc: batch x cols) of g^2, others the full second moment v. col_acc (batch x cols, all
+// zero between calls) and norm (batch) are scratch. chunk0: first 1024-element chunk of the
+// tensor in the update kernel's work list (ascending; update_chunks = total number of chunks);
+// finish_first[i]: first block of tensor i in the finish kernel (one block per batch entry of
+// every tensor, finish_blocks in total); max_tiles: the largest batch * ceil(rows / 16) of the
+// factored tensors (0: none is factored). sums as for vmoe_optimizer_step.
+typedef struct VmoeAdafactorTensor {
+  float* p;
+  const float* g;
+  float* mu;
+  void* shadow;
+  float* vr;
+  float* vc;
+  float* v;
+  float* col_acc;
+  float* norm;
+  int64_t batch, rows, cols;
+  float weight_decay, lr_mult, grad_scale;
+  int32_t factored, c_is_largest;
+  int64_t chunk0;
+} VmoeAdafactorTensor;
+VMOE_API int vmoe_adafactor_step(const VmoeAdafactorTensor* table, const int64_t* finish_first,
+                                 int32_t num_tensors, int64_t finish_blocks,
+                                 int64_t update_chunks, int64_t max_tiles, float decay, float eps,
+                                 float momentum, float lr, float clip_norm, float clip_value,
+                                 float grad_div, double* sums, vmoe_stream_t stream);
+
 // ----------------------------------------------------------------------------- attention
 // Non-causal softmax attention, bf16, head dim D a multiple of 16 up to 80, T queries and Tk keys
 // (keys and values of one head must fit shared memory: vmoe_attention_supported). q, k, v, dq, dk,

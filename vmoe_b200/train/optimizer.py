@@ -133,6 +133,17 @@ class _Bucket:
         p.grad = g
 
 
+class _AfTensor(ctypes.Structure):
+  """Mirror of ``VmoeAdafactorTensor`` (``csrc/vmoe_api.h``)."""
+  _fields_ = [("p", ctypes.c_void_p), ("g", ctypes.c_void_p), ("mu", ctypes.c_void_p),
+              ("shadow", ctypes.c_void_p), ("vr", ctypes.c_void_p), ("vc", ctypes.c_void_p),
+              ("v", ctypes.c_void_p), ("col_acc", ctypes.c_void_p), ("norm", ctypes.c_void_p),
+              ("batch", ctypes.c_int64), ("rows", ctypes.c_int64), ("cols", ctypes.c_int64),
+              ("weight_decay", ctypes.c_float), ("lr_mult", ctypes.c_float),
+              ("grad_scale", ctypes.c_float), ("factored", ctypes.c_int32),
+              ("c_is_largest", ctypes.c_int32), ("chunk0", ctypes.c_int64)]
+
+
 class Optimizer:
   """See the module docstring. ``named_params`` yields ``(flax_path, parameter)`` pairs."""
 
@@ -359,7 +370,95 @@ class Optimizer:
           st["v"] = torch.zeros_like(p.data)
         self.af_state[id(p)] = st
 
+  def _adafactor_cuda_plan(self):
+    """Table of tensors for the Adafactor kernels (built once), or None when a parameter is
+    factored over axes other than its last two (then the PyTorch formulation runs)."""
+    if getattr(self, "_af_plan", False) is not False:
+      return self._af_plan
+    self._af_plan = None
+    if next(iter(self.buckets.values())).device.type != "cuda" or not _lib.available():
+      return None
+    plans = {}
+    for kind, b in self.buckets.items():
+      rows, keep = [], []
+      chunk0 = finish0 = max_tiles = 0
+      finish_first = []
+      for i, (key, p) in enumerate(b.entries):
+        st = self.af_state[id(p)]
+        dims = _factored_dims(p.shape, self.af["min_dim_size_to_factor"])
+        t = _AfTensor()
+        pv, gv, mv = b.view_of(b.params, i), b.view_of(b.grads, i), b.view_of(b.mu, i)
+        t.p, t.g, t.mu = pv.data_ptr(), gv.data_ptr(), mv.data_ptr()
+        t.shadow = b.view_of(b.shadow, i).data_ptr() if b.shadow is not None else None
+        meta = b.meta[b.offsets[i] // CHUNK]
+        t.weight_decay, t.lr_mult, t.grad_scale = float(meta[0]), float(meta[1]), float(meta[2])
+        if dims is None:
+          t.factored, t.batch, t.rows, t.cols = 0, 1, 1, p.numel()
+          t.v = st["v"].data_ptr()
+        else:
+          d1, d0 = dims
+          nd = p.dim()
+          if {d1, d0} != {nd - 2, nd - 1}:
+            return None
+          t.factored, t.c_is_largest = 1, int(d0 == nd - 1)
+          t.rows, t.cols = p.shape[-2], p.shape[-1]
+          t.batch = p.numel() // (t.rows * t.cols)
+          over_cols = st["v_row"] if d0 == nd - 1 else st["v_col"]   # (.., rows)
+          over_rows = st["v_col"] if d0 == nd - 1 else st["v_row"]   # (.., cols)
+          assert over_cols.is_contiguous() and over_rows.is_contiguous()
+          col_acc = torch.zeros(t.batch * t.cols, device=p.device)
+          norm = torch.zeros(t.batch, device=p.device)
+          keep += [col_acc, norm]
+          t.vr, t.vc = over_cols.data_ptr(), over_rows.data_ptr()
+          t.col_acc, t.norm = col_acc.data_ptr(), norm.data_ptr()
+          max_tiles = max(max_tiles, t.batch * ((t.rows + 15) // 16))
+        t.chunk0 = chunk0
+        chunk0 += (p.numel() + 1023) // 1024
+        finish_first.append(finish0)
+        finish0 += t.batch
+        rows.append(t)
+      arr = (_AfTensor * len(rows))(*rows)
+      table = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(b.device)
+      first = torch.tensor(finish_first, dtype=torch.int64, device=b.device)
+      plans[kind] = dict(table=table, first=first, n=len(rows), finish_blocks=finish0,
+                         chunks=chunk0, max_tiles=max_tiles, keep=keep)
+    self._af_plan = plans
+    return plans
+
+  def _adafactor_step_cuda(self, plans, lr: float, grad_div: float):
+    af = self.af
+    tt = float(self.step_count - af["decay_offset"]) + 1.0
+    decay = min(af["decay_rate_max"], 1.0 - tt ** (-af["decay_rate"]))
+    dev = next(iter(self.buckets.values())).device
+    for b in self.buckets.values():
+      self._sumsq(b)   # sums[0] = sum of (grad * scale)^2, before the division by grad_div
+    g2 = {k: b.sums[0].clone() for k, b in self.buckets.items()}
+    zero = torch.zeros((), dtype=torch.float64, device=dev)
+    eg2 = g2.get("expert", zero)
+    if self.clip_norm > 0 and self._sharded():
+      eg2 = self._reduce_sum(eg2.clone().reshape(1), self.mesh.expert_group)[0]
+    total = g2.get("dense", zero) + eg2
+    f = ctypes.c_float
+    for kind, b in self.buckets.items():
+      pl = plans[kind]
+      b.sums[0] = total   # the kernels read the global norm for the clip
+      rc = _lib.lib().vmoe_adafactor_step(
+          _vp(pl["table"].data_ptr()), _vp(pl["first"].data_ptr()), ctypes.c_int32(pl["n"]),
+          ctypes.c_int64(pl["finish_blocks"]), ctypes.c_int64(pl["chunks"]),
+          ctypes.c_int64(pl["max_tiles"]), f(decay), f(af["eps"]), f(af["momentum"] or 0.0),
+          f(lr), f(self.clip_norm), f(self.clip_value), f(grad_div), _vp(b.sums.data_ptr()),
+          _vp(_lib.stream_ptr()))
+      _lib.check(rc, "vmoe_adafactor_step")
+      _lib.count_launch(3)
+    div2 = grad_div * grad_div
+    pack = lambda k: (torch.stack([g2[k] / div2, self.buckets[k].sums[1], self.buckets[k].sums[2]])
+                      if k in self.buckets else torch.zeros(3, dtype=torch.float64, device=dev))
+    return pack("dense"), pack("expert")
+
   def _adafactor_step(self, lr: float, grad_div: float):
+    plans = self._adafactor_cuda_plan()
+    if plans is not None:
+      return self._adafactor_step_cuda(plans, lr, grad_div)
     af = self.af
     step = self.step_count
     tt = float(step - af["decay_offset"]) + 1.0
