@@ -346,9 +346,10 @@ def main() -> int:
                       and args.ensemble_size == 1 else
                       f"{args.model}, mode={args.mode}, ensemble_size={args.ensemble_size}"),
             "global_batch": batch * world,
-            "seq_len": 197,
+            "seq_len": (IMAGE_SIZE // int(cfg.patch_size[0])) ** 2 + 1,
             "parallelism": f"dp{world} x ep{num_partitions}",
-            "l2": "no flush needed: per-step inputs (353 MB) and activations (GBs) exceed the 126 MB L2",
+            "l2": (f"no flush needed: per-step inputs ({batch * (IMAGE_SIZE * IMAGE_SIZE * 3 + NUM_CLASSES) * 4 / 1e6:.0f} MB per GPU) "
+                   "and activations (GBs) exceed the 126 MB L2"),
         },
         "clocks": clocks,
         "e2e": e2e,
