@@ -4,10 +4,13 @@
 Every rank owns one expert and the buffers XE (rows pushed to its expert), YB (expert outputs
 coming home), DYE and DXB (the same for the backward pass), with monotone counters: per-tile
 arrival counters that gate the first GEMM (target ``epoch * rows``) and per-source completion
-counters that gate the combine (target ``epoch``). A barrier at the start of every forward
-pass separates the steps. Each rank is a coroutine on one in-order stream; a seeded random
-scheduler interleaves the ranks. Cells carry a tag (what, step) so that a read of stale or
-too-new data is seen. Leaving out the barrier or either kind of wait makes the model fail.
+counters that gate the combine (target ``epoch``). Steps are separated by "free" counters
+instead of a barrier: after its last read of XE / DYE in a backward pass (the weight
+gradients) an owner bumps its entry of every rank's free counters, and a rank's next forward
+pass pushes only once every owner has done so. Each rank is a coroutine on one in-order
+stream; a seeded random scheduler interleaves the ranks. Cells carry a tag (what, step) so
+that a read of stale or too-new data is seen. Leaving out the free wait or either other kind
+of wait makes the model fail.
 """
 import random
 
@@ -32,7 +35,7 @@ class Layer:
     self.fdy = [[0] * world for _ in range(world)]
     self.fy = [[0] * world for _ in range(world)]    # [home][expert]
     self.fdx = [[0] * world for _ in range(world)]
-    self.barrier_count = 0
+    self.ffree = [[0] * world for _ in range(world)]  # [pusher][owner]
 
 
 def _expect(cell, what, step, who):
@@ -47,10 +50,10 @@ def rank_program(c, q, steps, skip=None):
   x_of = lambda step, src, owner, row: step * 1000 + src * 100 + owner * 10 + row
   for step in range(1, steps + 1):
     # ------------------------------------------------------------------ forward
-    c.barrier_count += 1
-    if skip != "barrier":
-      while c.barrier_count < step * w:
-        yield
+    if skip != "free":
+      for owner in range(w):
+        while c.ffree[q][owner] < step - 1:
+          yield
     # push my rows for every expert into its owner's XE, then bump the tile's counter
     for i in range(w):
       owner = (q + i) % w
@@ -114,6 +117,9 @@ def rank_program(c, q, steps, skip=None):
         _expect(c.xe[q][src][row], "x", step, f"wgrad of rank {q}")
         _expect(c.dye[q][src][row], "dy", step, f"wgrad of rank {q}")
       yield
+    # ... for the last time: every pusher may overwrite what it sent to this owner
+    for src in range(w):
+      c.ffree[src][q] += 1
     for e in range(w):
       if skip != "complete":
         while c.fdx[q][e] < step:
@@ -150,9 +156,10 @@ def test_protocol_is_correct_under_random_schedules(world, rows):
     c = run(world, rows, steps=3, seed=seed)
     assert all(v == 3 * rows for row in c.fx for v in row)
     assert all(v == 3 for row in c.fy for v in row)
+    assert all(v == 3 for row in c.ffree for v in row)
 
 
-@pytest.mark.parametrize("skip", ["barrier", "arrival", "complete"])
+@pytest.mark.parametrize("skip", ["free", "arrival", "complete"])
 def test_model_detects_a_missing_wait(skip):
   failures = 0
   for seed in range(80):

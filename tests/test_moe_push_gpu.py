@@ -1,5 +1,5 @@
-"""The bulk-copy row push (``csrc/moe_push.cuh``) alone and as the push CTAs of the expert GEMM,
-on one GPU: the destination tables point at local buffers laid out as the expert owners' buffers
+"""The bulk-copy row push (``csrc/moe_push.cuh``) alone and as the push warps inside the CTAs
+of the expert GEMM, on one GPU: the destination tables point at local buffers laid out as the expert owners' buffers
 would be, so the row movement, the zero rows of empty slots, the tile counters, the gate scaling
 and the gate gradients can be compared with the plain gather formulation in PyTorch."""
 import pytest
