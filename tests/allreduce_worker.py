@@ -36,6 +36,7 @@ def run(mesh, device, use_p2p, rank, steps=3):
   status = 0
   if state.optimizer.grad_reducer is not None:
     status = int(state.optimizer.grad_reducer.status.item())
+    state.optimizer.grad_reducer.buf.check_guards("gradient all-reduce buffer")
     ranges = state.optimizer.grad_reducer.num_ranges
     state.optimizer.grad_reducer.deactivate()
   else:

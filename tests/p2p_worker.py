@@ -199,6 +199,8 @@ def main():
     oracle_errs[name] = rel_errs(got, want)
   soft_comms = sum(1 for k in moe_ops._LAYER_COMMS)
   status = [int(cm.status.item()) for cm in moe_ops._LAYER_COMMS.values()]
+  for cm in moe_ops._LAYER_COMMS.values():
+    cm.check_guards()  # nothing was stored between or past the peer-written regions
   json.dump({"errs": results, "oracle_errs": oracle_errs, "status": status,
              "layer_comms": soft_comms},
             open(os.path.join(outdir, f"p2p_r{rank}.json"), "w"))

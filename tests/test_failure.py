@@ -80,3 +80,20 @@ def test_store_barrier_can_reuse_a_name():
   with pytest.raises(failure.BarrierTimeout) as e:
     failure.store_barrier("epoch", timeout_s=0.05, store=store, rank=0, world_size=2, poll_s=0.01)
   assert e.value.missing == [1]
+
+
+def test_canary_words_around_peer_written_regions():
+  """Guard words of a (here: plain CPU) buffer: intact after writes inside the regions, reported
+  by offset after a write that runs one element past a region or copies a neighbouring guard."""
+  from vmoe_b200.parallel import symm
+  buf = torch.zeros(4096, dtype=torch.uint8)
+  offsets = [0, 1024 + symm.GUARD_BYTES, 4096 - symm.GUARD_BYTES]
+  symm.write_guards(buf, offsets)
+  buf[symm.GUARD_BYTES:offsets[1]] = 7           # the whole first region
+  buf[offsets[1] + symm.GUARD_BYTES:offsets[2]] = 9
+  assert symm.damaged_guards(buf, offsets) == []
+  buf[offsets[1]] = 7                            # one byte too far
+  assert symm.damaged_guards(buf, offsets) == [offsets[1]]
+  symm.write_guards(buf, offsets)
+  buf[offsets[2]:] = buf[:symm.GUARD_BYTES].clone()   # a guard copied over another
+  assert symm.damaged_guards(buf, offsets) == [offsets[2]]

@@ -194,11 +194,18 @@ class LayerComm:
     blk = e * r * h * 2
     fl_tiles = (self.el * self.tiles * 4 + 255) // 256 * 256
     fl_src = 256
-    self.off = {"XE": 0, "YB": blk, "DYE": 2 * blk, "DXB": 3 * blk,
-                "FX": 4 * blk, "FDY": 4 * blk + fl_tiles, "FY": 4 * blk + 2 * fl_tiles,
-                "FDX": 4 * blk + 2 * fl_tiles + fl_src,
-                "FFREE": 4 * blk + 2 * fl_tiles + 2 * fl_src}
-    self.buf = symm.SymmetricBuffer(4 * blk + 2 * fl_tiles + 3 * fl_src, exchange.group, device)
+    # Canary words before, between and after the four data regions and after the counters: a
+    # peer's store that runs past its block lands in one of them (``check_guards``).
+    gb = symm.GUARD_BYTES
+    blk_g = blk + gb
+    fl0 = gb + 4 * blk_g
+    self.off = {"XE": gb, "YB": gb + blk_g, "DYE": gb + 2 * blk_g, "DXB": gb + 3 * blk_g,
+                "FX": fl0, "FDY": fl0 + fl_tiles, "FY": fl0 + 2 * fl_tiles,
+                "FDX": fl0 + 2 * fl_tiles + fl_src,
+                "FFREE": fl0 + 2 * fl_tiles + 2 * fl_src}
+    end = fl0 + 2 * fl_tiles + 3 * fl_src
+    self.buf = symm.SymmetricBuffer(end + gb, exchange.group, device)
+    self.buf.set_guards([0] + [self.off[k] + blk for k in ("XE", "YB", "DYE", "DXB")] + [end])
     self.rank = self.buf.rank
     b = self.buf
     self.xe = b.local(self.off["XE"], (self.el, ep * r, h), torch.bfloat16)
@@ -230,6 +237,11 @@ class LayerComm:
     self.yb_table = _base_table(self.yb)
     self.dxb_table = _base_table(self.dxb)
     self.mt_offset = (self.rank * r) // 128
+
+  def check_guards(self) -> None:
+    """Raises ``symm.BufferOverrun`` if something wrote between or past the regions of this
+    rank's buffer (synchronises with the device)."""
+    self.buf.check_guards("expert exchange buffers")
 
   def home_out(self, key: str, src: int) -> torch.Tensor:
     """View of source rank ``src``'s YB/DXB slice that receives this rank's experts."""

@@ -109,9 +109,12 @@ class OverlappedGradReducer:
       self.range_ids = {FINAL_TAG: [0]}
     self.num_ranges = len(self.ranges)
     grad_bytes = bucket.numel * 4
-    self.flag_off = (grad_bytes + 255) // 256 * 256
-    nbytes = self.flag_off + 3 * self.num_ranges * 4
-    self.buf = symm.SymmetricBuffer(nbytes, group, device=bucket.device)
+    # Canary words between the gradients and the counters and after the counters.
+    guard0 = (grad_bytes + 255) // 256 * 256
+    self.flag_off = guard0 + symm.GUARD_BYTES
+    guard1 = (self.flag_off + 3 * self.num_ranges * 4 + 255) // 256 * 256
+    self.buf = symm.SymmetricBuffer(guard1 + symm.GUARD_BYTES, group, device=bucket.device)
+    self.buf.set_guards([guard0, guard1])
     new_grads = self.buf.local(0, (bucket.numel,), torch.float32)
     new_grads.copy_(bucket.grads)
     bucket.grads = new_grads

@@ -290,19 +290,22 @@ def wrap_train_step_with_adversarial_attack(train_step_fn, loss_fn, *, max_epsil
 
 def check_device_status(state: TrainState) -> None:
   """Raises ``failure.DeviceWaitTimeout`` if a kernel of the peer-memory paths (expert exchange,
-  gradient all-reduce) recorded a wait that ran out since the last check. Reading the status
+  gradient all-reduce) recorded a wait that ran out since the last check, and
+  ``symm.BufferOverrun`` if the canary words around a peer-written region changed. Reading the status
   words synchronises with the device, so the training loop calls this only every
   ``check_device_status_every_steps`` steps."""
   from vmoe_b200.parallel import failure
   reducer = getattr(state.optimizer, "grad_reducer", None) if state.optimizer else None
   if reducer is not None:
     failure.check_status(reducer.status, "gradient all-reduce")
+    reducer.buf.check_guards("gradient all-reduce buffer")
   try:
     from vmoe_b200.ops import moe_ops
   except Exception:  # pylint: disable=broad-except
     return
   for comm in getattr(moe_ops, "_LAYER_COMMS", {}).values():
     failure.check_status(comm.status, "expert exchange")
+    comm.check_guards()
 
 
 def create_checkpoint_manager(*, workdir: str, every_steps: Optional[int] = None,
