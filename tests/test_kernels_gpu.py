@@ -1,4 +1,5 @@
 """Elementwise / MoE / loss / optimizer kernels vs PyTorch fp32 references."""
+import copy
 import math
 
 import pytest
@@ -258,6 +259,60 @@ def test_adafactor_kernels_match_the_pytorch_formulation(clip):
                                  msg=f"p{i}/{name}")
 
 
+def _rel_l2(a, b):
+  a, b = a.detach().float().cpu(), b.detach().float().cpu()
+  return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("description", ["ViT-S/32, E=8, K=2, Last 2", "ViT-S/32, E=4, K=1, Every 2"])
+def test_model_on_kernels_matches_fp32_pytorch_model(description):
+  """A whole V-MoE (patch embedding, attention, LayerNorms, routers, dispatch, experts, head)
+  on the bf16 kernels against the same weights through fp32 PyTorch ops: logits, auxiliary loss
+  and the gradients of a loss with respect to parameters of every kind. Routing is discrete, so
+  a token whose two best experts are nearly tied may go elsewhere in bf16; the comparison is a
+  relative L2 error over whole tensors, which a few such tokens do not move."""
+  from vmoe_b200 import models as models_lib
+  from vmoe_b200.configs.vmoe_paper import common
+  torch.manual_seed(0)
+  cfg = common.get_vmoe_config(description, 224, 100)
+  cfg.encoder.moe.router.dispatcher.batch_priority = True
+  cfg.encoder.dtype = "bfloat16"
+  fast = models_lib.create_model(cfg, deterministic=True, image_size=224).to(DEV)
+  cfg32 = copy.deepcopy(cfg)
+  cfg32.encoder.dtype = "float32"
+  slow = models_lib.create_model(cfg32, deterministic=True, image_size=224).to(DEV)
+  slow.load_state_dict(fast.state_dict())
+  # Nonzero head, so that the logits say something about the encoder.
+  with torch.no_grad():
+    for m in (fast, slow):
+      torch.manual_seed(1)
+      m.head.weight.normal_(0, 0.05)
+  images = torch.rand(16, 224, 224, 3, device=DEV) * 2 - 1
+  labels = F.one_hot(torch.randint(0, 100, (16,), device=DEV), 100).float()
+
+  def run(model, kernels):
+    with ops.use_cuda_kernels(kernels):
+      logits, metrics = model(images)
+      loss = F.cross_entropy(logits.float(), labels) + metrics["auxiliary_loss"].float().mean()
+      model.zero_grad(set_to_none=True)
+      loss.backward()
+    return logits, metrics["auxiliary_loss"], {n: p.grad for n, p in model.named_parameters()}
+
+  logits_f, aux_f, grads_f = run(fast, True)
+  logits_s, aux_s, grads_s = run(slow, False)
+  assert _rel_l2(logits_f, logits_s) < 3e-2
+  assert _rel_l2(aux_f, aux_s) < 2e-2
+  checked = 0
+  for name, g in grads_s.items():
+    if g is None or g.norm() == 0:
+      continue
+    assert grads_f[name] is not None, name
+    err = _rel_l2(grads_f[name], g)
+    assert err < 8e-2, (name, err)
+    checked += 1
+  assert checked > 40
+
+
 def test_graft_smoke():
   import __graft_entry__
   __graft_entry__.smoke()
@@ -511,11 +566,6 @@ def test_allreduce_range_with_a_peer_that_never_arrives():
   torch.cuda.synchronize()
   assert status.item() & 32
   assert torch.equal(mine, torch.ones(n, device=DEV))  # nothing was reduced
-  # With both "ranks" run in turn (one kernel pair each, epoch 2) the sum is exchanged.
-  status.zero_()
-  for f in flags:
-    f.zero_()
-  local.zero_()
 
 
 def test_qk_norm_on_packed_qkv():

@@ -5,7 +5,11 @@
 Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with residual),
 ``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
 ``gemm_multi_dest`` (second expert GEMM storing row blocks into eight destination buffers),
-``layernorm`` (forward and backward), ``attention`` (packed-QKV forward and backward),
+``gemm_library`` (the same shapes through ``torch.matmul`` / ``torch.addmm``, i.e. cuBLAS: the
+comparator of the two cases above), ``layernorm`` (forward and backward), ``attention``
+(packed-QKV forward and backward at the B/16 shape: 12 heads of 64, 197 tokens),
+``attention_h14`` (16 heads of 80, 257 tokens: the key-blocked kernels, with PyTorch's fused
+attention as the comparator), ``attention_dropout`` (the B/16 shape with dropout 0.1),
 ``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward),
 ``soft_router`` (Soft MoE dispatch / combine softmaxes, forward and backward).
 Every case runs one warm-up pass, then times ``iters`` passes with CUDA events; inputs are
@@ -134,6 +138,61 @@ def attention(rows: int, iters: int):
         f"bwd: {us_b:.1f} us ({2.5 * flops / us_b / 1e6:.0f} TFLOP/s useful)")
 
 
+def gemm_library(rows: int, iters: int):
+  """The shapes of ``gemm_dense`` / ``gemm_dgrad`` through cuBLAS (``torch.matmul``, and
+  ``torch.addmm`` for the bias): the rate a library GEMM reaches WITHOUT the GELU, the second
+  output, the residual add or the column sums that our epilogues carry."""
+  dev = "cuda"
+  x = torch.randn(rows, 768, device=dev).bfloat16()
+  for name, n in (("qkv", 2304), ("fc1", 3072), ("out_proj", 768)):
+    w = torch.randn(n, 768, device=dev).bfloat16()
+    b = torch.randn(n, device=dev).bfloat16()
+    out = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+    flops = 2 * rows * 768 * n
+    us = _timed(lambda: torch.matmul(x, w.t(), out=out), iters)
+    us_b = _timed(lambda: torch.addmm(b, x, w.t(), out=out), iters)
+    print(f"library {name}: matmul {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s; with bias "
+          f"{us_b:.1f} us, {flops / us_b / 1e6:.0f} TFLOP/s")
+  w2 = torch.randn(768, 3072, device=dev).bfloat16()
+  out = torch.empty(rows, 3072, device=dev, dtype=torch.bfloat16)
+  us = _timed(lambda: torch.matmul(x, w2, out=out), iters)
+  print(f"library dgrad (rows x 768) x (768 x 3072): {us:.1f} us, "
+        f"{2 * rows * 768 * 3072 / us / 1e6:.0f} TFLOP/s")
+
+
+def _attention_case(batch, t, h, d, iters, dropout=0.0, library=True):
+  from vmoe_b200 import ops
+  import torch.nn.functional as F
+  qkv = torch.randn(batch, t, 3, h, d, device="cuda").bfloat16().requires_grad_()
+  run = lambda: ops.attention_packed(qkv, dropout_p=dropout, training=dropout > 0)
+  out = run()
+  g = torch.randn_like(out)
+  us_f = _timed(run, iters)
+  us_b = _timed(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), iters)
+  flops = 4 * batch * h * t * t * d
+  line = (f"attention B={batch} T={t} H={h} D={d} dropout={dropout}: fwd {us_f:.1f} us "
+          f"({flops / us_f / 1e6:.0f} TFLOP/s useful); bwd {us_b:.1f} us "
+          f"({2.5 * flops / us_b / 1e6:.0f} TFLOP/s useful)")
+  if library:
+    q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+    lib = lambda: F.scaled_dot_product_attention(q, k, v, dropout_p=dropout)
+    out2 = lib()
+    g2 = torch.randn_like(out2)
+    us_lf = _timed(lib, iters)
+    us_lb = _timed(lambda: torch.autograd.grad(out2, qkv, g2, retain_graph=True), iters)
+    line += f"; PyTorch fused attention fwd {us_lf:.1f} us, bwd {us_lb:.1f} us"
+  print(line)
+
+
+def attention_h14(rows: int, iters: int):
+  """ViT-H/14 at 224 px: 16 heads of 80, 257 tokens (two key blocks, head dimension not 64)."""
+  _attention_case(max(rows // 257 // 4, 1), 257, 16, 80, iters)
+
+
+def attention_dropout(rows: int, iters: int):
+  _attention_case(max(rows // 197, 1), 197, 12, 64, iters, dropout=0.1)
+
+
 def router(rows: int, iters: int):
   from vmoe_b200.models import routing
   groups = 32
@@ -177,8 +236,10 @@ def soft_router(rows: int, iters: int):
         f"{us_tb:.1f} us)")
 
 
-CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad, "gemm_multi_dest": gemm_multi_dest, "layernorm": layernorm, "attention": attention,
-         "router": router}
+CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad,
+         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "layernorm": layernorm,
+         "attention": attention, "attention_h14": attention_h14,
+         "attention_dropout": attention_dropout, "router": router}
 
 
 def main():
