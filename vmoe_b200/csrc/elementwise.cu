@@ -458,7 +458,21 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long
   const bool ok = chunk * 8 < n;
   if (ok) {
     const __nv_bfloat16* base = x + (static_cast<long long>(b) * rows) * n + chunk * 8;
-    for (long long r = r0 + rlane; r < r1; r += 8) {
+    // Four independent 16-byte loads per thread and trip keep enough bytes in flight per SM.
+    long long r = r0 + rlane;
+    for (; r + 24 < r1; r += 32) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = __ldg(reinterpret_cast<const uint4*>(base + (r + 8 * u) * n));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(q[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+    }
+    for (; r < r1; r += 8) {
       float f[8];
       unpack8(__ldg(reinterpret_cast<const uint4*>(base + r * n)), f);
 #pragma unroll

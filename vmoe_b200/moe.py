@@ -28,6 +28,9 @@ Tensor = torch.Tensor
 
 
 # --------------------------------------------------------------------------------- capacity
+_CAPACITY_WARNED: set = set()
+
+
 def compute_capacity(num_tokens: int, num_experts: int, capacity_factor: float,
                      ceil_or_round: str = "ceil", multiple_of: Optional[int] = 4) -> int:
   """Slots per expert needed to spread ``num_tokens`` over ``num_experts``."""
@@ -45,7 +48,10 @@ def compute_capacity(num_tokens: int, num_experts: int, capacity_factor: float,
   if multiple_of and multiple_of > 0:
     capacity += (-capacity) % multiple_of
   actual = capacity * num_experts / num_tokens
-  if abs(actual - capacity_factor) > 1e-6:
+  key = (capacity_factor, num_tokens, num_experts, multiple_of)
+  if abs(actual - capacity_factor) > 1e-6 and key not in _CAPACITY_WARNED:
+    # Once per geometry: the reference logs this while tracing, i.e. once per compiled step.
+    _CAPACITY_WARNED.add(key)
     logging.warning(
         "The target capacity_factor is %f, but with num_tokens=%d and num_experts=%d the "
         "actual capacity_factor is %f.", capacity_factor, num_tokens, num_experts, actual)

@@ -6,7 +6,7 @@ Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with r
 ``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
 ``gemm_multi_dest`` (second expert GEMM storing row blocks into eight destination buffers),
 ``gemm_library`` (the same shapes through ``torch.matmul`` / ``torch.addmm``, i.e. cuBLAS: the
-comparator of the two cases above), ``layernorm`` (forward and backward), ``attention``
+comparator of the two cases above), ``colsum`` (bias gradients), ``layernorm`` (forward and backward), ``attention``
 (packed-QKV forward and backward at the B/16 shape: 12 heads of 64, 197 tokens),
 ``attention_h14`` (16 heads of 80, 257 tokens: the key-blocked kernels, with PyTorch's fused
 attention as the comparator), ``attention_dropout`` (the B/16 shape with dropout 0.1),
@@ -104,6 +104,16 @@ def gemm_multi_dest(rows: int, iters: int):
   }.items():
     us = _timed(fn, iters)
     print(f"{name}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+
+
+def colsum(rows: int, iters: int):
+  """Bias gradients: column sums of (rows, n) bf16 matrices into fp32."""
+  from vmoe_b200.ops import reduce
+  for n in (768, 2304, 3072):
+    x = torch.randn(rows, n, device="cuda").bfloat16()
+    out = torch.zeros(n, device="cuda")
+    us = _timed(lambda: reduce.colsum(x, out=out), iters)
+    print(f"colsum rows x {n}: {us:.1f} us ({rows * n * 2 / us / 1e3:.0f} GB/s)")
 
 
 def layernorm(rows: int, iters: int):
@@ -237,7 +247,7 @@ def soft_router(rows: int, iters: int):
 
 
 CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad,
-         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "layernorm": layernorm,
+         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "colsum": colsum, "layernorm": layernorm,
          "attention": attention, "attention_h14": attention_h14,
          "attention_dropout": attention_dropout, "router": router}
 
