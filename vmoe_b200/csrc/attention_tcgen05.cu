@@ -138,7 +138,11 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* e) {
 }
 
 #ifdef ATT_TRACE
-// Timing probes (experiments only): CTA 0 records clock64 at tagged points.
+// Timing probes (builds with -DATT_TRACE only): CTA 0 records clock64 at tagged points, read
+// back with vmoe_attention_trace_read (python -m vmoe_b200.ops.bench_kernels attention_trace).
+// Forward tags, softmax warp: 0 before / 1 after the wait for S, 2 after the row maximum, 3 after
+// P is written, 4 after the wait for O, 5 after the output is stored; MMA thread: 0 / 1 around
+// the wait for Q and K, 4 when the item's products are issued, 5 when they have retired.
 __device__ long long g_att_trace[2][4096];
 __device__ int g_att_trace_n[2];
 #define ATT_STAMP(who, tag)                                                         \
@@ -282,7 +286,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       }
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
         const int next = item + gridDim.x;
+        ATT_STAMP(1, 0);
         ATT_WAIT(bar_qk, n_item & 1, kStatusTimeoutMma | (1u << (7 + 1)));
+        ATT_STAMP(1, 1);
         for (int kb = 0; kb < L.nkb && ok; ++kb) {
           const int nk = min(ATT_KBLOCK, tk16 - kb * ATT_KBLOCK);
           // S (and, aliased, O) columns are free once the softmax warps have read them.
@@ -337,7 +343,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         // (one per key block), which a waiter that is not in step with them cannot tell apart,
         // so this thread has a barrier of its own with one phase per item.
         umma_commit(bar_done);
+        ATT_STAMP(1, 4);
         if (ok) ATT_WAIT(bar_done, n_item & 1, kStatusTimeoutMma | (1u << 15));
+        ATT_STAMP(1, 5);
         if (ok && next < n_items) {
           if (L.aliased) load_qk(next);
           load_v(next);
@@ -367,7 +375,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         const int nk = min(ATT_KBLOCK, tk16 - kb * ATT_KBLOCK);
         const int key0 = kb * ATT_KBLOCK;
         const int n32 = (nk + 31) / 32;
+        if (warp == 1) ATT_STAMP(0, 0);
         ATT_WAIT_WARP(bar_s, n_s & 1, kStatusTimeoutEpilogue);
+        if (warp == 1) ATT_STAMP(0, 1);
         ++n_s;
         if (!ok) break;
         tc_fence_after();
@@ -406,6 +416,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         }
         m_run = mx;
         const float mxs = mx * sl2;
+        if (warp == 1) ATT_STAMP(0, 2);
         for (int c = 0; c < n32; ++c) {
           const int chunk = c >> 1, slot = chunk % L.np;
           if ((c & 1) == 0) {
@@ -458,7 +469,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         }
       }
       if (!ok) break;
+      if (warp == 1) ATT_STAMP(0, 3);
       ATT_WAIT_WARP(bar_o, n_o & 1, kStatusTimeoutEpilogue);
+      if (warp == 1) ATT_STAMP(0, 4);
       ++n_o;
       if (!ok) break;
       tc_fence_after();
@@ -481,6 +494,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         if (q < p.Tq && p.lse)
           p.lse[(static_cast<long long>(b) * p.H + h) * p.Tq + q] = m_run * p.scale + __logf(l_run);
       }
+      if (warp == 1) ATT_STAMP(0, 5);
       tc_fence_before();
       mbar_arrive(bar_sfree);  // O (and the last S) have been read: the next item may start
     }
@@ -1241,7 +1255,9 @@ extern "C" int vmoe_attention_bwd(const VmoeAttnArgs* a, vmoe_stream_t stream_) 
 }
 
 #ifdef ATT_TRACE
-extern "C" int vmoe_attention_trace_read(long long* out, int who) {
+// Copies the stamps of role `who` (0 softmax warp, 1 MMA thread) as (tag, clock) pairs into
+// `out` (4096 values), resets the list and returns the number of stamps.
+extern "C" VMOE_API int vmoe_attention_trace_read(long long* out, int who) {
   int n = 0;
   cudaMemcpyFromSymbol(&n, g_att_trace_n, sizeof(int), who * sizeof(int));
   cudaMemcpyFromSymbol(out, g_att_trace, sizeof(long long) * 4096, who * 4096 * sizeof(long long));

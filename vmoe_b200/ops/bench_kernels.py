@@ -8,7 +8,7 @@ Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with r
 ``gemm_library`` (the same shapes through ``torch.matmul`` / ``torch.addmm``, i.e. cuBLAS: the
 comparator of the two cases above), ``colsum`` (bias gradients), ``layernorm`` (forward and backward), ``attention``
 (packed-QKV forward and backward at the B/16 shape: 12 heads of 64, 197 tokens),
-``attention_h14`` (16 heads of 80, 257 tokens: the key-blocked kernels, with PyTorch's fused
+``attention_trace`` (in-kernel timeline, diagnostic build), ``attention_h14`` (16 heads of 80, 257 tokens: the key-blocked kernels, with PyTorch's fused
 attention as the comparator), ``attention_dropout`` (the B/16 shape with dropout 0.1),
 ``router`` (gating logits, noisy softmax, auxiliary losses, forward and backward),
 ``soft_router`` (Soft MoE dispatch / combine softmaxes, forward and backward).
@@ -194,6 +194,49 @@ def _attention_case(batch, t, h, d, iters, dropout=0.0, library=True):
   print(line)
 
 
+def attention_trace(rows: int, iters: int):
+  """In-kernel timeline of one CTA of the general attention kernels (needs a library built with
+  ``python -m vmoe_b200.build --define ATT_TRACE=1 --output <path>`` and loaded through
+  ``VMOE_B200_LIB=<path>``): mean cycles between consecutive probes, by (tag, next tag), for the
+  forward pass and for the backward pass; the tags are listed beside ``ATT_STAMP`` in
+  ``csrc/attention_tcgen05.cu``. Set ``VMOE_B200_ATTN_GENERAL=1`` for the D = 64 shape."""
+  import collections
+  import ctypes
+  from vmoe_b200.ops import _lib, attention_ops
+  lib = _lib.lib()
+  if not hasattr(lib, "vmoe_attention_trace_read"):
+    raise SystemExit("this library was built without -DATT_TRACE")
+  batch = max(rows // 197, 1)
+  qkv = torch.randn(batch, 197, 3, 12, 64, device="cuda").bfloat16().requires_grad_()
+  buf = (ctypes.c_longlong * 4096)()
+
+  def report(title):
+    for who, name in ((0, "softmax warp"), (1, "MMA thread")):
+      n = lib.vmoe_attention_trace_read(buf, who)
+      ev = [(buf[2 * i], buf[2 * i + 1]) for i in range(n)]
+      if not ev:
+        continue
+      print(f"{title}, {name}: {n} stamps over {ev[-1][1] - ev[0][1]} cycles")
+      acc = collections.defaultdict(list)
+      for (t0, c0), (t1, c1) in zip(ev, ev[1:]):
+        acc[t0, t1].append(c1 - c0)
+      for (t0, t1), v in sorted(acc.items()):
+        v = v[2:] if len(v) > 4 else v
+        print(f"  {t0} -> {t1}: n={len(v)} mean={sum(v) / len(v):.0f} min={min(v)} max={max(v)}")
+
+  out = attention_ops.packed_attention(qkv)
+  g = torch.randn_like(out)
+  torch.cuda.synchronize()
+  for who in (0, 1):
+    lib.vmoe_attention_trace_read(buf, who)
+  out = attention_ops.packed_attention(qkv)
+  torch.cuda.synchronize()
+  report("forward")
+  out.backward(g)
+  torch.cuda.synchronize()
+  report("backward")
+
+
 def attention_h14(rows: int, iters: int):
   """ViT-H/14 at 224 px: 16 heads of 80, 257 tokens (two key blocks, head dimension not 64)."""
   _attention_case(max(rows // 257 // 4, 1), 257, 16, 80, iters)
@@ -248,7 +291,7 @@ def soft_router(rows: int, iters: int):
 
 CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad,
          "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "colsum": colsum, "layernorm": layernorm,
-         "attention": attention, "attention_h14": attention_h14,
+         "attention": attention, "attention_trace": attention_trace, "attention_h14": attention_h14,
          "attention_dropout": attention_dropout, "router": router}
 
 
