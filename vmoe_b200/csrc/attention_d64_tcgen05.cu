@@ -49,6 +49,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint
       : "memory");
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Bounded wait used by every role; on failure all roles fall through to the common exit.
 #undef ATT_WAIT
 #define ATT_WAIT(bar, parity, code)                                              \
@@ -75,8 +81,14 @@ struct AttnParams {
 
 // ================================================================================ forward
 // smem: [V: BNx128B (<=32 KiB)] [P: 4 x 16 KiB, the first 16+32 KiB double as Q and K]
-constexpr int FWD_THREADS = 160;
-constexpr int FWD_SMEM = 32768 + 65536 + 1024 + 128;
+// Warp 0 loads and issues the MMAs; eight softmax warps, two threads per query row (a warp's TMEM
+// lane quadrant is its index modulo 4): warps 1-4 take the even 32-key chunks of the row, warps
+// 5-8 the odd ones, and the two exchange their partial row maximum and row sum through shared
+// memory. Two CTAs share an SM, so every scheduler has four softmax warps to interleave.
+constexpr int FWD_THREADS = 288;
+constexpr int FWD_SOFTMAX_THREADS = 256;
+constexpr int FWD_XCHG_BYTES = 2 * 2 * 128 * 4;  // [max | sum][half][row]
+constexpr int FWD_SMEM = 32768 + 65536 + 1024 + 128 + FWD_XCHG_BYTES;
 
 __global__ void __launch_bounds__(FWD_THREADS, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -91,19 +103,21 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 32768 + 65536);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(smem + 32768 + 65536 + 128);
   unsigned* status = p.status;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const uint32_t bar_qk = smem_u32(bars), bar_v = smem_u32(bars + 1), bar_s = smem_u32(bars + 2),
-                 bar_p = smem_u32(bars + 3), bar_o = smem_u32(bars + 4);
+                 bar_p = smem_u32(bars + 3), bar_o = smem_u32(bars + 4), bar_mx = smem_u32(bars + 5);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_qk, 1);
     mbar_init(bar_v, 1);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_p, FWD_SOFTMAX_THREADS);
     mbar_init(bar_o, 1);
+    mbar_init(bar_mx, FWD_SOFTMAX_THREADS);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -150,10 +164,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   } else {
     // ---------------------------------------------------------------- softmax / epilogue
     const int quad = warp & 3;
+    const int half = (warp - 1) >> 2;      // 0: even 32-key chunks of the row, 1: odd ones
     const int r = quad * 32 + lane;        // row inside the query tile
     const int q = qt * ATT_TILE + r;       // query index
     const uint32_t trow = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     const float sl2 = p.scale * kLog2e;
+    const uint32_t rx = static_cast<uint32_t>(r) & 7u;
+    float* xmax = xchg;            // [half][row]
+    float* xsum = xchg + 2 * 128;  // [half][row]
     {
       const bool got = mbar_wait(bar_s, 0, abort_flag, status, kStatusTimeoutEpilogue);
       ok = __all_sync(0xffffffffu, got);
@@ -162,24 +180,69 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     if (ok) {
       tc_fence_after();
       const int nchunk = (BN + 31) / 32;
-      for (int c = 0; c < nchunk; ++c) {
+      // Row maximum over this thread's chunks; the key bound is tested only where key T falls.
+      for (int c = half; c < nchunk; c += 2) {
         uint32_t v[32];
         tmem_ld_32x32(trow + c * 32, v);
         tmem_ld_wait();
+        const int valid = p.T - c * 32;
+        if (valid >= 32) {
+          float m0 = mx, m1 = mx, m2 = mx, m3 = mx;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < p.T) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; i += 8) {
+            m0 = max3(m0, __uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+            m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+            m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
       }
+      // The other thread of the row holds the maximum of the other chunks.
+      xmax[half * 128 + r] = mx;
+      mbar_arrive(bar_mx);
+      const bool got = mbar_wait(bar_mx, 0, abort_flag, status, kStatusTimeoutEpilogue);
+      ok = __all_sync(0xffffffffu, got);
+    }
+    if (ok) {
+      mx = fmaxf(mx, xmax[(half ^ 1) * 128 + r]);
       const float mxs = mx * sl2;
-      for (int c = 0; c < nchunk; ++c) {
+      const int nchunk = (BN + 31) / 32;
+      const f32x2 sl = f2_pack(sl2, sl2), ms = f2_pack(-mxs, -mxs);
+      for (int c = half; c < nchunk; c += 2) {
         uint32_t v[32];
         tmem_ld_32x32(trow + c * 32, v);
         tmem_ld_wait();
         float e[32];
+        const int valid = p.T - c * 32;
+        if (valid >= 32) {
+          f32x2 s0 = f2_pack(0.f, 0.f), s1 = s0;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          e[i] = (c * 32 + i < p.T) ? exp2f(__uint_as_float(v[i]) * sl2 - mxs) : 0.f;
-          sum += e[i];
+          for (int i = 0; i < 32; i += 4) {
+            float a0, a1, a2, a3;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sl, ms), a0, a1);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), sl, ms), a2,
+                      a3);
+            e[i] = exp2f(a0);
+            e[i + 1] = exp2f(a1);
+            e[i + 2] = exp2f(a2);
+            e[i + 3] = exp2f(a3);
+            s0 = f2_add(s0, f2_pack(e[i], e[i + 1]));
+            s1 = f2_add(s1, f2_pack(e[i + 2], e[i + 3]));
+          }
+          float a0, a1;
+          f2_unpack(f2_add(s0, s1), a0, a1);
+          sum += a0 + a1;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            e[i] = i < valid ? exp2f(__uint_as_float(v[i]) * sl2 - mxs) : 0.f;
+            sum += e[i];
+          }
         }
         // Row r of the 64-key chunk (c / 2): 16-byte units j = 4 * (c & 1) + i, 128B swizzle.
         uint8_t* base = sP + (c >> 1) * ATT_TILE_BYTES + r * ATT_ROW_BYTES;
@@ -191,9 +254,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
           u.z = pack_bf16x2(e[8 * i + 4], e[8 * i + 5]);
           u.w = pack_bf16x2(e[8 * i + 6], e[8 * i + 7]);
           const uint32_t j = static_cast<uint32_t>(4 * (c & 1) + i);
-          *reinterpret_cast<uint4*>(base + ((j ^ (static_cast<uint32_t>(r) & 7u)) << 4)) = u;
+          *reinterpret_cast<uint4*>(base + ((j ^ rx) << 4)) = u;
         }
       }
+      xsum[half * 128 + r] = sum;  // visible to the row's other thread once bar_o completes
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_p);
@@ -202,10 +266,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     }
     if (ok) {
       tc_fence_after();
+      sum += xsum[(half ^ 1) * 128 + r];
       const float inv = 1.0f / sum;
       __nv_bfloat16* orow = p.out + b * p.o_batch + static_cast<long long>(q) * p.o_tok + h * p.o_head;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
+        const int c = half;  // 32 of the 64 output columns per thread
         uint32_t v[32];
         tmem_ld_32x32(trow + c * 32, v);
         tmem_ld_wait();
@@ -221,7 +286,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
           }
         }
       }
-      if (q < p.T && p.lse)
+      if (half == 0 && q < p.T && p.lse)
         p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q] = mx * p.scale + __logf(sum);
     }
   }
