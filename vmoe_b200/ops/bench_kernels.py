@@ -5,6 +5,7 @@
 Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with residual),
 ``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
 ``gemm_multi_dest`` (second expert GEMM storing row blocks into eight destination buffers),
+``gemm_expert_wgrad`` (weight gradients of batched experts, accumulating and not),
 ``gemm_library`` (the same shapes through ``torch.matmul`` / ``torch.addmm``, i.e. cuBLAS: the
 comparator of the two cases above), ``colsum`` (bias gradients), ``layernorm`` (forward and backward), ``attention``
 (packed-QKV forward and backward at the B/16 shape: 12 heads of 64, 197 tokens),
@@ -146,6 +147,25 @@ def attention(rows: int, iters: int):
   flops = 4 * batch * 12 * 197 * 197 * 64
   print(f"attention fwd: {us_f:.1f} us ({flops / us_f / 1e6:.0f} TFLOP/s useful); "
         f"bwd: {us_b:.1f} us ({2.5 * flops / us_b / 1e6:.0f} TFLOP/s useful)")
+
+
+def gemm_expert_wgrad(rows: int, iters: int):
+  """Weight-gradient GEMMs of batched experts, dW[e] = dy[e]^T x[e], adding into an fp32 buffer
+  (``accumulate=True``, as the backward pass does) and as a plain store: many small experts
+  (Soft MoE B/16: 128 x 256 and 128 x 512 rows, V-MoE L/16: 32 x 832 rows) and the 8 large
+  experts of V-MoE B/16."""
+  from vmoe_b200.ops import gemm as G
+  for e, r, h, m in ((128, 256, 768, 3072), (128, 512, 768, 3072), (32, 832, 1024, 4096),
+                     (8, 26624, 768, 3072)):
+    dy = torch.randn(e, r, m, device="cuda").bfloat16()
+    x = torch.randn(e, r, h, device="cuda").bfloat16()
+    dw = torch.zeros(e, m, h, device="cuda")
+    flops = 2.0 * e * r * h * m
+    for acc in (True, False):
+      us = _timed(lambda: G.gemm(dy, x, a_mn_major=True, b_mn_major=True, out=dw, accumulate=acc),
+                  iters)
+      print(f"experts={e} rows={r} weight {m}x{h} accumulate={acc}: {us:.0f} us, "
+            f"{flops / us / 1e6:.0f} TFLOP/s")
 
 
 def gemm_library(rows: int, iters: int):
@@ -290,7 +310,7 @@ def soft_router(rows: int, iters: int):
 
 
 CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad,
-         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "colsum": colsum, "layernorm": layernorm,
+         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "gemm_expert_wgrad": gemm_expert_wgrad, "colsum": colsum, "layernorm": layernorm,
          "attention": attention, "attention_trace": attention_trace, "attention_h14": attention_h14,
          "attention_dropout": attention_dropout, "router": router}
 
