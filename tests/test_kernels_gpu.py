@@ -478,8 +478,12 @@ def test_layer_norm_fork_adds_residual_gradient():
   _close(b.grad, b2.grad, 1e-2)
 
 
+@pytest.mark.parametrize("slots", [0, 1])
 @pytest.mark.parametrize("g,s,n,h", [(5, 196, 128, 768), (3, 50, 16, 64), (2, 197, 264, 128)])
-def test_einsum_dispatch_combine_on_gemm(g, s, n, h):
+def test_einsum_dispatch_combine_on_gemm(g, s, n, h, slots):
+  """``slots`` = 1: the dispatch output and the gradient of the combine input are laid out
+  expert-major in memory, and the combine / the dispatch backward read such strided views in
+  place (the path of a one-slot Soft MoE layer, here with the expert-major round trip)."""
   from vmoe_b200.ops import einsum_ops
   torch.manual_seed(0)
   logits = torch.randn(g, s, n, device=DEV)
@@ -487,8 +491,16 @@ def test_einsum_dispatch_combine_on_gemm(g, s, n, h):
   wc = torch.softmax(logits, dim=2).requires_grad_()
   x = torch.randn(g, s, h, device=DEV).bfloat16().requires_grad_()
   assert einsum_ops.supported(wd, x)
-  xe = einsum_ops.dispatch(wd, x)
-  out = einsum_ops.combine(wc, xe)
+  xe = einsum_ops.dispatch(wd, x, slots_per_expert=slots)
+  if slots == 1:
+    assert xe.transpose(0, 1).is_contiguous()
+    # (G, N, H) -> experts' view (N, G, H) -> back, as the layer does around the expert MLP
+    ye = xe.transpose(0, 1).reshape(n, g, h) * 1.0
+    xe_in = ye.reshape(n, g, 1, h).transpose(0, 1).reshape(g, n, h)
+    assert not xe_in.is_contiguous()
+  else:
+    xe_in = xe
+  out = einsum_ops.combine(wc, xe_in, slots_per_expert=slots)
   probe = torch.randn_like(out)
   (out.float() * probe.float()).sum().backward()
   wd2, wc2 = wd.detach().clone().requires_grad_(), wc.detach().clone().requires_grad_()

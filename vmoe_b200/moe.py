@@ -155,7 +155,8 @@ class EinsumDispatcher(BaseDispatcher):
     flat = data.reshape(g, s, -1)
     w2 = w.reshape(g, s, e * c)
     if _einsum_ops().supported(w2, flat):
-      out = _einsum_ops().dispatch(w2 if w2.is_floating_point() else w2.to(flat.dtype), flat)
+      out = _einsum_ops().dispatch(w2 if w2.is_floating_point() else w2.to(flat.dtype), flat,
+                                   slots_per_expert=c)
     else:
       out = torch.einsum("gsn,gsh->gnh", w2.to(flat.dtype), flat)
     return _to_experts(out.reshape(g, e, c, *data.shape[2:]), self.exchange)
@@ -166,7 +167,7 @@ class EinsumDispatcher(BaseDispatcher):
     flat = x.reshape(g, e * c, -1)
     w2 = self.combine_weights.reshape(g, s, e * c)
     if _einsum_ops().supported(w2, flat):
-      out = _einsum_ops().combine(w2, flat)
+      out = _einsum_ops().combine(w2, flat, slots_per_expert=c)
     else:
       out = torch.einsum("gsn,gnh->gsh", w2.to(flat.dtype), flat)
     return out.reshape(g, s, *x.shape[3:])
