@@ -164,10 +164,22 @@ class _LinearFn(torch.autograd.Function):
 
 
 def _wgrad_split(n: int, k: int, m: int) -> int:
-  tiles = ((n + 127) // 128) * ((k + 255) // 256)
-  if tiles >= 120 or m < 4096:
+  """Split-K factor of a weight-gradient GEMM with an (n, k) output and contraction length m.
+
+  The output has few 256 x 256 tiles (27 for the qkv weights of ViT-B) against 74 CTA pairs, so
+  the contraction is cut into pieces that fill whole rounds of the machine. The cost of a
+  factor is rounds / factor plus 1.5 % per piece (each piece adds its tile to the output with
+  atomics); the cheapest factor wins."""
+  tiles = ((n + 255) // 256) * ((k + 255) // 256)
+  pairs = 74
+  if tiles >= 2 * pairs or m < 4096:
     return 1
-  return max(1, min(148 // tiles, m // 2048))
+  best, best_cost = 1, -(-tiles // pairs) + 0.015
+  for split in range(2, max(1, min(16, m // 2048)) + 1):
+    cost = -(-tiles * split // pairs) / split + 0.015 * split
+    if cost < best_cost:
+      best, best_cost = split, cost
+  return best
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
