@@ -49,6 +49,26 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint
       : "memory");
 }
 
+#ifdef ATT_TRACE
+// Timing probes of the backward kernel (builds with -DATT_TRACE only): the CTA of batch 0, head 0
+// records clock64 at tagged points; vmoe_attention_d64_trace_read returns them. Tags, softmax
+// warp: 0 rows' delta / lse loaded, 1 S and dP of a step have arrived, 2 P and dS written, 3 the
+// step's products have retired (end of a key half), 4 dV / dK stored, 5 dQ stored; MMA thread:
+// 0 operands in shared memory, 1 S / dP issued, 2 P / dS arrived, 3 dV / dK / dQ products issued.
+__device__ long long g_d64_trace[2][4096];
+__device__ int g_d64_trace_n[2];
+#define D64_STAMP(who, tag)                                                                  \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && g_d64_trace_n[who] < 2040) {     \
+      const int i_ = g_d64_trace_n[who]++;                                                   \
+      g_d64_trace[who][2 * i_] = (tag);                                                      \
+      g_d64_trace[who][2 * i_ + 1] = clock64();                                              \
+    }                                                                                        \
+  } while (0)
+#else
+#define D64_STAMP(who, tag) do {} while (0)
+#endif
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -361,6 +381,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tma_load_4d(smem_u32(sV + i * ATT_TILE_BYTES), &tv, bar_ld, 0, h, i * ATT_TILE, b);
       }
       ATT_WAIT(bar_ld, 0, kStatusTimeoutMma);
+      D64_STAMP(1, 0);
       int it = 0;
       for (int kh = 0; kh < n_kh && ok; ++kh) {
         const int nk = min(ATT_TILE, BN - kh * ATT_TILE);  // keys in this half (multiple of 16)
@@ -390,7 +411,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
             umma_bf16(tmem + TM_DP, umma_smem_desc(dobase + k * 32, 16, 1024),
                       umma_smem_desc(vbase + k * 32, 16, 1024), id_s, k > 0);
           umma_commit(bar_s);
+          D64_STAMP(1, 1);
           ATT_WAIT(bar_p, it & 1, kStatusTimeoutMma);
+          D64_STAMP(1, 2);
           if (!ok) break;
           tc_fence_after();
           // dV[kh] += P^T dO, dK[kh] += dS^T Q: A read MN-major (M = keys), B MN-major (N = d).
@@ -413,6 +436,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
                       umma_smem_desc(kbase + k * 2048, ATT_TILE_BYTES, 1024), id_q,
                       (kh > 0 || k > 0));
           umma_commit(bar_mma);
+          D64_STAMP(1, 3);
         }
       }
       // Final: make sure the last MMAs retired before the epilogue reads dV/dK/dQ.
@@ -448,6 +472,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       }
     }
     int it = 0;
+    if (warp == 1) D64_STAMP(0, 0);
     for (int kh = 0; kh < n_kh && ok; ++kh) {
       const int nk = min(ATT_TILE, BN - kh * ATT_TILE);
       for (int qt = 0; qt < n_qt && ok; ++qt, ++it) {
@@ -455,6 +480,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
           const bool got = mbar_wait(bar_s, it & 1, abort_flag, status, kStatusTimeoutEpilogue);
           ok = __all_sync(0xffffffffu, got);
         }
+        if (warp == 1) D64_STAMP(0, 1);
         if (!ok) break;
         tc_fence_after();
         const int q = qt * ATT_TILE + r;
@@ -509,6 +535,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         fence_proxy_async();
         tc_fence_before();
         mbar_arrive(bar_p);
+        if (warp == 1) D64_STAMP(0, 2);
       }
       if (!ok) break;
       // dV / dK of this key half are complete once the last step's MMAs retire.
@@ -517,6 +544,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         ok = __all_sync(0xffffffffu, got);
       }
       if (!ok) break;
+      if (warp == 1) D64_STAMP(0, 3);
       tc_fence_after();
       const int key = kh * ATT_TILE + r;
       const long long goff = b * p.g_batch + static_cast<long long>(key) * p.g_tok + h * p.g_head;
@@ -543,6 +571,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       }
       tc_fence_before();
       mbar_arrive(bar_acc);
+      if (warp == 1) D64_STAMP(0, 4);
     }
     if (ok) {
       // dQ of both query tiles (accumulated over the key halves).
@@ -568,6 +597,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
           }
         }
       }
+      if (warp == 1) D64_STAMP(0, 5);
     }
   }
   tc_fence_before();
@@ -722,3 +752,17 @@ int attention_d64_bwd(const VmoeAttnArgs* a, vmoe_stream_t stream_) {
   return 0;
 }
 }  // namespace vmoe
+
+#ifdef ATT_TRACE
+// Copies the stamps of role `who` (0 softmax warp, 1 MMA thread) of the one-shot backward kernel
+// as (tag, clock) pairs into `out` (4096 values), resets the list, returns the number of stamps.
+extern "C" VMOE_API int vmoe_attention_d64_trace_read(long long* out, int who) {
+  int n = 0;
+  cudaMemcpyFromSymbol(&n, vmoe::d64::g_d64_trace_n, sizeof(int), who * sizeof(int));
+  cudaMemcpyFromSymbol(out, vmoe::d64::g_d64_trace, sizeof(long long) * 4096,
+                       who * 4096 * sizeof(long long));
+  int zero = 0;
+  cudaMemcpyToSymbol(vmoe::d64::g_d64_trace_n, &zero, sizeof(int), who * sizeof(int));
+  return n;
+}
+#endif

@@ -20,6 +20,7 @@ under ``profiles/``.
 from __future__ import annotations
 
 import argparse
+import os
 
 import torch
 
@@ -219,7 +220,9 @@ def attention_trace(rows: int, iters: int):
   ``python -m vmoe_b200.build --define ATT_TRACE=1 --output <path>`` and loaded through
   ``VMOE_B200_LIB=<path>``): mean cycles between consecutive probes, by (tag, next tag), for the
   forward pass and for the backward pass; the tags are listed beside ``ATT_STAMP`` in
-  ``csrc/attention_tcgen05.cu``. Set ``VMOE_B200_ATTN_GENERAL=1`` for the D = 64 shape."""
+  ``csrc/attention_tcgen05.cu``. With ``VMOE_B200_ATTN_GENERAL=1`` the D = 64 shape runs on the
+  general kernels; without it, on the one-shot kernels, whose backward pass carries probes of
+  its own (``csrc/attention_d64_tcgen05.cu``)."""
   import collections
   import ctypes
   from vmoe_b200.ops import _lib, attention_ops
@@ -230,9 +233,12 @@ def attention_trace(rows: int, iters: int):
   qkv = torch.randn(batch, 197, 3, 12, 64, device="cuda").bfloat16().requires_grad_()
   buf = (ctypes.c_longlong * 4096)()
 
+  general = os.environ.get("VMOE_B200_ATTN_GENERAL") == "1"
+  reader = lib.vmoe_attention_trace_read if general else lib.vmoe_attention_d64_trace_read
+
   def report(title):
     for who, name in ((0, "softmax warp"), (1, "MMA thread")):
-      n = lib.vmoe_attention_trace_read(buf, who)
+      n = reader(buf, who)
       ev = [(buf[2 * i], buf[2 * i + 1]) for i in range(n)]
       if not ev:
         continue
@@ -248,7 +254,7 @@ def attention_trace(rows: int, iters: int):
   g = torch.randn_like(out)
   torch.cuda.synchronize()
   for who in (0, 1):
-    lib.vmoe_attention_trace_read(buf, who)
+    reader(buf, who)
   out = attention_ops.packed_attention(qkv)
   torch.cuda.synchronize()
   report("forward")
