@@ -6,6 +6,7 @@ Cases: ``gemm_dense`` (qkv, fc1 with GELU and two outputs, out-projection with r
 ``gemm_dgrad`` (hidden-gradient GEMM with / without GELU' and column sums in the epilogue),
 ``gemm_multi_dest`` (second expert GEMM storing row blocks into eight destination buffers),
 ``gemm_expert_wgrad`` (weight gradients of batched experts, accumulating and not),
+``gemm_dense_wgrad`` (weight gradients of the dense layers over split-K factors),
 ``gemm_library`` (the same shapes through ``torch.matmul`` / ``torch.addmm``, i.e. cuBLAS: the
 comparator of the two cases above), ``colsum`` (bias gradients), ``layernorm`` (forward and backward), ``attention``
 (packed-QKV forward and backward at the B/16 shape: 12 heads of 64, 197 tokens),
@@ -169,6 +170,26 @@ def gemm_expert_wgrad(rows: int, iters: int):
             f"{flops / us / 1e6:.0f} TFLOP/s")
 
 
+def gemm_dense_wgrad(rows: int, iters: int):
+  """Weight gradients of the dense layers of ViT-B, dW = dy^T x over ``rows`` tokens, adding
+  into an fp32 buffer with the split-K factor the backward pass picks
+  (``ops/functional.py:_wgrad_split``) and with factors 1, 2, 4 and 8 for comparison."""
+  from vmoe_b200.ops import gemm as G
+  from vmoe_b200.ops.functional import _wgrad_split
+  for name, n, k in (("qkv", 2304, 768), ("out_proj", 768, 768), ("fc1", 3072, 768),
+                     ("fc2", 768, 3072)):
+    dy = torch.randn(rows, n, device="cuda").bfloat16()
+    x = torch.randn(rows, k, device="cuda").bfloat16()
+    dw = torch.zeros(n, k, device="cuda")
+    picked = _wgrad_split(n, k, rows)
+    parts = []
+    for split in sorted({picked, 1, 2, 4, 8}):
+      us = _timed(lambda: G.gemm(dy, x, a_mn_major=True, b_mn_major=True, out=dw,
+                                 accumulate=True, split_k=split), iters)
+      parts.append(f"split {split}{' (picked)' if split == picked else ''}: {us:.0f} us")
+    print(f"{name} weight gradient {n}x{k}: " + ", ".join(parts))
+
+
 def gemm_library(rows: int, iters: int):
   """The shapes of ``gemm_dense`` / ``gemm_dgrad`` through cuBLAS (``torch.matmul``, and
   ``torch.addmm`` for the bias): the rate a library GEMM reaches WITHOUT the GELU, the second
@@ -316,7 +337,7 @@ def soft_router(rows: int, iters: int):
 
 
 CASES = {"soft_router": soft_router, "gemm_dense": gemm_dense, "gemm_dgrad": gemm_dgrad,
-         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "gemm_expert_wgrad": gemm_expert_wgrad, "colsum": colsum, "layernorm": layernorm,
+         "gemm_multi_dest": gemm_multi_dest, "gemm_library": gemm_library, "gemm_expert_wgrad": gemm_expert_wgrad, "gemm_dense_wgrad": gemm_dense_wgrad, "colsum": colsum, "layernorm": layernorm,
          "attention": attention, "attention_trace": attention_trace, "attention_h14": attention_h14,
          "attention_dropout": attention_dropout, "router": router}
 
