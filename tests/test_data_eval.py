@@ -57,6 +57,26 @@ def test_prefetch_to_device_passthrough_on_cpu():
   assert [float(o["x"].mean()) for o in out] == [0.0, 1.0, 2.0]
 
 
+def test_prefetch_transforms_match_the_host_value_range_op():
+  """uint8 images mapped to [-1, 1] by the prefetcher equal the host-side ``value_range`` op;
+  uint8 labels are cast. (On a GPU the same functions run on the copy stream.)"""
+  from vmoe_b200.data import pp_ops
+  rng = np.random.default_rng(0)
+  images = rng.integers(0, 256, size=(3, 2, 8, 8, 3), dtype=np.uint8)
+  labels = rng.integers(0, 2, size=(3, 2, 5), dtype=np.uint8)
+  data = [{"image": images[i], "labels": labels[i]} for i in range(3)]
+  out = list(pjit_utils.prefetch_to_device(
+      iter(data), size=2, device=torch.device("cpu"),
+      dtypes={"labels": torch.float32},
+      transforms={"image": pjit_utils.value_range_on_device(-1.0, 1.0)}))
+  host_op = pp_ops.value_range(-1, 1)
+  for i, o in enumerate(out):
+    want = np.stack([host_op({"image": img})["image"] for img in images[i]])
+    assert o["image"].dtype == torch.float32 and o["labels"].dtype == torch.float32
+    np.testing.assert_allclose(o["image"].numpy(), want, atol=1e-6)
+    np.testing.assert_array_equal(o["labels"].numpy(), labels[i].astype(np.float32))
+
+
 def test_ensemble_losses_reduce_to_plain_losses_for_identical_members():
   torch.manual_seed(0)
   logits = torch.randn(4, 7)

@@ -85,3 +85,28 @@ def test_microsteps_and_mixup_run(tmp_path):
   config.extra_rng_keys = ("dropout", "gating", "mixup")
   state, metrics = trainer.train_and_evaluate(config, str(tmp_path), mesh=mesh, writer=_Writer())
   assert state.step == 2 and torch.isfinite(torch.as_tensor(metrics["total_loss"]))
+
+
+def test_device_value_range_option(tmp_path):
+  """``dataset.train.device_value_range``: the pipeline leaves the images uint8 (no
+  ``value_range`` in its process string) and the prefetcher maps them behind the copy."""
+  mesh = mesh_lib.get_auto_logical_mesh(1)
+  mesh_lib.set_mesh(mesh)
+  config = _config(2)
+  pp = 'onehot(5, inkey="label", outkey="labels")|keep("image", "labels")'
+  config.dataset.train.process = pp
+  config.dataset.train.device_value_range = (-1.0, 1.0)
+  seen = {}
+  orig = trainer.train_step
+
+  def spy(state, images, labels, *a, **k):
+    seen["dtype"], seen["min"], seen["max"] = images.dtype, float(images.min()), float(images.max())
+    return orig(state, images, labels, *a, **k)
+
+  trainer.train_step = spy
+  try:
+    state, metrics = trainer.train_and_evaluate(config, str(tmp_path), mesh=mesh, writer=_Writer())
+  finally:
+    trainer.train_step = orig
+  assert state.step == 2 and torch.isfinite(torch.as_tensor(metrics["total_loss"]))
+  assert seen["dtype"] == torch.float32 and -1.0 - 1e-6 <= seen["min"] < seen["max"] <= 1.0 + 1e-6

@@ -12,7 +12,7 @@ from __future__ import annotations
 import logging
 import queue
 import threading
-from typing import Any, Callable, Dict, Iterable, Iterator, Mapping, Optional, Union
+from typing import Sequence, Any, Callable, Dict, Iterable, Iterator, Mapping, Optional, Union
 
 import numpy as np
 import torch
@@ -131,8 +131,11 @@ def get_dataset(*, variant: str, name: str, split: str, batch_size: int, process
                 prefetch: Optional[Union[int, str]] = None,
                 shuffle_buffer: int = DEFAULT_SHUFFLE_BUFFER,
                 shuffle_seed: Optional[int] = None, prefetch_device: Optional[int] = None,
+                device_value_range: Optional[Sequence[float]] = None,
                 **extra_builder_kwargs) -> DatasetIterator:
-  del num_parallel_calls, prefetch_device  # threads / device prefetch are handled elsewhere
+  # Threads / device prefetch are handled elsewhere; ``device_value_range`` is read by the
+  # training loop (uint8 images mapped on the GPU, ``data/pjit_utils.py``).
+  del num_parallel_calls, prefetch_device, device_value_range
   if variant == "train" and shuffle_seed is not None:
     logging.error(
         "Deterministic training is not supported but you specified shuffle_seed=%d for "
@@ -231,6 +234,6 @@ def get_datasets(config: Mapping[str, Any]) -> Dict[str, DatasetIterator]:
 def get_data_num_examples(config: Mapping[str, Any]) -> int:
   cfg = config.to_dict() if hasattr(config, "to_dict") else dict(config)
   pipeline_keys = ("variant", "batch_size", "process", "cache", "num_parallel_calls", "prefetch",
-                   "prefetch_device", "shuffle_buffer", "pre_filter_fn")
+                   "prefetch_device", "shuffle_buffer", "pre_filter_fn", "device_value_range")
   builder_kwargs = {k: v for k, v in cfg.items() if k not in pipeline_keys}
   return builder_lib.get_dataset_builder(**builder_kwargs).num_examples

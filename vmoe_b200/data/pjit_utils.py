@@ -9,7 +9,7 @@ goes to the local device. Batches are staged in pinned host memory and copied wi
 from __future__ import annotations
 
 import collections
-from typing import Any, Dict, Iterable, Iterator, Mapping, Optional
+from typing import Any, Callable, Dict, Iterable, Iterator, Mapping, Optional
 
 import numpy as np
 import torch
@@ -48,21 +48,55 @@ class _PinnedPool:
     return buf
 
 
+def value_range_on_device(vmin: float = -1.0, vmax: float = 1.0, in_min: float = 0.0,
+                          in_max: float = 255.0,
+                          dtype: torch.dtype = torch.float32) -> Callable[[torch.Tensor], torch.Tensor]:
+  """The ``value_range`` preprocessing op as a transform for ``prefetch_to_device``: images
+  travel to the GPU as the uint8 the decoder produced (a quarter of the bytes of float32) and
+  are mapped to ``[vmin, vmax]`` there, on the copy stream. The host-side pipeline then leaves
+  ``value_range`` out (``vmoe/data/pp_ops.py`` applies it on the host in the reference)."""
+  scale = (vmax - vmin) / (in_max - in_min)
+  offset = vmin - in_min * scale
+  offsets: Dict[Any, torch.Tensor] = {}
+
+  def transform(x: torch.Tensor) -> torch.Tensor:
+    # offset + scale * x in one pass: the 0-dim float operand promotes the result, the uint8
+    # input is read as it is (one kernel instead of cast, multiply, add).
+    off = offsets.get(x.device)
+    if off is None:
+      off = offsets[x.device] = torch.full((), offset, dtype=dtype, device=x.device)
+    return torch.add(off, x, alpha=scale)
+
+  return transform
+
+
 def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
                        device: Optional[torch.device] = None,
-                       dtypes: Optional[Mapping[str, torch.dtype]] = None
+                       dtypes: Optional[Mapping[str, torch.dtype]] = None,
+                       transforms: Optional[Mapping[str, Callable[[torch.Tensor], torch.Tensor]]] = None
                        ) -> Iterator[Dict[str, torch.Tensor]]:
   """Yields batches whose tensors live on ``device``; ``size`` copies are kept in flight.
 
-  On a CPU-only machine (or ``device`` = cpu) batches are passed through as tensors.
+  ``dtypes[name]`` casts a tensor after its copy and ``transforms[name]`` maps it (e.g.
+  ``value_range_on_device``), both on the copy stream, so that compact host formats (uint8
+  images, uint8 multi-hot labels) cross PCIe and the step sees what it expects.
+  On a CPU-only machine (or ``device`` = cpu) batches are passed through as tensors (cast and
+  transformed the same way).
   """
   if device is None:
     device = (torch.device("cuda", torch.cuda.current_device())
               if torch.cuda.is_available() else torch.device("cpu"))
   device = torch.device(device)
+  def finish(k, t):
+    if dtypes and k in dtypes:
+      t = t.to(dtypes[k])
+    if transforms and k in transforms:
+      t = transforms[k](t)
+    return t
+
   if device.type != "cuda":
     for batch in iterator:
-      yield {k: _to_tensor(v) for k, v in batch.items()}
+      yield {k: finish(k, _to_tensor(v)) for k, v in batch.items()}
     return
   stream = torch.cuda.Stream(device=device)
   pool = _PinnedPool(size)
@@ -117,8 +151,9 @@ def prefetch_to_device(iterator: Iterable[Mapping[str, Any]], size: int = 2,
         if ev_free is not None:
           stream.wait_event(ev_free)
         d.copy_(t, non_blocking=True)
-        if dtypes and k in dtypes:
-          d = d.to(dtypes[k])
+        if (dtypes and k in dtypes) or (transforms and k in transforms):
+          # A new tensor made on the copy stream and consumed on the compute stream.
+          d = finish(k, d)
           d.record_stream(torch.cuda.current_stream(device))
         out[k] = d
       ev = torch.cuda.Event()

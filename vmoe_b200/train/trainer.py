@@ -798,8 +798,17 @@ def train_and_evaluate(config, workdir: str, mesh: Optional[mesh_lib.Mesh] = Non
     it = iter(datasets["train"])
     while True:
       yield next(it)
+  # ``dataset.train.device_value_range = (vmin, vmax)``: the pipeline delivers uint8 images
+  # (its ``process`` string leaves ``value_range`` out) and they are mapped to [vmin, vmax] on
+  # the GPU after the copy; multi-hot / one-hot labels may arrive as uint8 as well.
+  transforms, dtypes = None, None
+  dvr = config.dataset.train.get("device_value_range")
+  if dvr:
+    transforms = {"image": pjit_utils.value_range_on_device(float(dvr[0]), float(dvr[1]))}
+    dtypes = {"labels": torch.float32}
   tr_iter = pjit_utils.prefetch_to_device(
-      batches(), size=int(config.dataset.train.get("prefetch_device", 2) or 2), device=device)
+      batches(), size=int(config.dataset.train.get("prefetch_device", 2) or 2), device=device,
+      dtypes=dtypes, transforms=transforms)
 
   status_every = int(config.get("check_device_status_every_steps", 100) or 100)
   # Optional host-side failure detection (``config.heartbeat = {every_steps, timeout_seconds}``).
