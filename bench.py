@@ -54,6 +54,9 @@ def parse_args():
   ap.add_argument("--ensemble-size", type=int, default=1,
                   help=">1: the ensemble-of-experts variant (inputs repeated per member, experts "
                        "split into that many groups)")
+  ap.add_argument("--num-partitions", type=int, default=0,
+                  help="size of the 'expert' mesh axis (default: all GPUs, at most 8); smaller "
+                       "values replicate every expert shard over world / num_partitions ranks")
   return ap.parse_args()
 
 
@@ -193,7 +196,9 @@ def main() -> int:
   if not args.library_ops:
     _lib.lib()  # the CUDA library must be present on a GPU box
 
-  num_partitions = min(8, world)
+  num_partitions = args.num_partitions or min(8, world)
+  if world % num_partitions:
+    raise SystemExit(f"--num-partitions {num_partitions} does not divide {world} GPUs")
   mesh = mesh_lib.get_auto_logical_mesh(num_partitions)
   mesh_lib.set_mesh(mesh)
 
