@@ -13,9 +13,13 @@ def _rand(*shape):
 
 
 def _check(out, ref, tol=2e-2):
+  """Largest error relative to the largest reference value, and the relative L2 error over the
+  whole tensor (which a wrong tile or a missing edge moves even when no element is far off)."""
   err = (out.float() - ref.float()).abs().max().item()
   scale = ref.float().abs().max().item() + 1e-6
   assert err / scale < tol, (err, scale)
+  rel_l2 = ((out.float() - ref.float()).norm() / (ref.float().norm() + 1e-12)).item()
+  assert rel_l2 < tol, ("relative L2", rel_l2)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (512, 768, 768), (200, 304, 136), (1000, 21843, 192)])
