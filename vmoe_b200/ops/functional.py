@@ -61,6 +61,8 @@ def _grad_target(p: torch.Tensor):
   """The fp32 gradient buffer of a parameter if one is bound (flat optimizer buffers), so the
   weight-gradient GEMM can accumulate into it in place instead of going through autograd's
   allocate + add."""
+  if not p.is_leaf:
+    return None  # an intermediate result used as a weight: autograd owns its gradient
   g = getattr(p, "grad", None)
   if (g is not None and g.dtype == torch.float32 and g.shape == p.shape and g.is_contiguous()
       and not g.requires_grad):
