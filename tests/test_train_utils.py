@@ -194,3 +194,20 @@ def test_hardware_and_logical_mesh_views():
   assert np.array_equal(lm4, np.asarray(mesh_lib.mesh_layout(16, 4)))
   x = object()
   assert partitioning.with_sharding_constraint(x, ("expert",)) is x
+
+
+def test_weight_gradient_split_factor_fills_whole_rounds_of_cta_pairs():
+  """``_wgrad_split`` cuts the contraction of a weight-gradient GEMM so that tiles x pieces fill
+  whole rounds of the 74 CTA pairs: 27 tiles (qkv of ViT-B) take 5 pieces (135 items, two rounds),
+  9 tiles (out-projection) take 8, 36 tiles (fc1 / fc2) take 2 (72 of 74 pairs); large outputs
+  and short contractions are not split."""
+  from vmoe_b200.ops.functional import _wgrad_split
+  rows = 512 * 197
+  assert _wgrad_split(2304, 768, rows) == 5
+  assert _wgrad_split(768, 768, rows) == 8
+  assert _wgrad_split(3072, 768, rows) == 2 and _wgrad_split(768, 3072, rows) == 2
+  assert _wgrad_split(21843, 768, rows) == 1      # 258 tiles: more than two rounds already
+  assert _wgrad_split(2304, 768, 2048) == 1       # too few rows to be worth cutting
+  for n, k in ((1024, 1024), (3840, 1280), (512, 512)):
+    s = _wgrad_split(n, k, rows)
+    assert 1 <= s <= 16 and s <= rows // 2048
